@@ -6,6 +6,9 @@ One tensor per page group holds the keys and values of all its caches:
 ``[n_embd_gqa, n_cells]`` per layer (src/iian/kv_cache.cpp:163-164); the cell numbering
 (page * page_size + offset, include/iian/kv_cache.h:135-137) is the same.
 
+A cache that keeps one row per token (``RowNeed``: a latent every head reads) is
+``[caches, pages, page_size, width]``; its cells are numbered the same way.
+
 Fixed-size state: one tensor ``[slots, *shape]`` per cache that asked for it, zeroed when a slot is
 handed to a new request.
 """
@@ -16,7 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import KVNeed, StateNeed
+from ..parts.base import KVNeed, RowNeed, StateNeed, is_paged
 from .manager import PageGroup
 
 
@@ -28,24 +31,31 @@ class KVView:
 
 
 @dataclass
+class RowView:
+    group: int            # index of the page group
+    rows: torch.Tensor    # [pages, page_size, width]
+
+
+@dataclass
 class StateView:
     state: torch.Tensor   # [slots, *shape]
 
 
 def plan_groups(needs: Dict[int, object], capacity_tokens: int, block_size: int,
                 window_tokens: Optional[int] = None) -> Tuple[List[PageGroup], List[KVNeed]]:
-    """Group caches with the same KV need.  ``capacity_tokens`` sizes a group that keeps all keys;
+    """Group caches with the same paged need (``KVNeed`` or ``RowNeed``).  ``capacity_tokens`` sizes a group that keeps all keys;
     a windowed group gets ``window_tokens`` if given (else the same)."""
-    by_need: Dict[KVNeed, List[int]] = {}
+    by_need: Dict[object, List[int]] = {}
     for cid in sorted(needs):
         need = needs[cid]
-        if isinstance(need, KVNeed):
+        if is_paged(need):
             by_need.setdefault(need, []).append(cid)
     groups, kinds = [], []
     for need, cids in by_need.items():
         tokens = capacity_tokens if need.window is None or window_tokens is None else min(capacity_tokens, window_tokens)
         n_blocks = max(1, (tokens + block_size - 1) // block_size)
-        name = f"kv{need.num_kv_heads}x{need.head_dim}" + (f"w{need.window}" if need.window else "")
+        name = (f"kv{need.num_kv_heads}x{need.head_dim}" if isinstance(need, KVNeed) else f"row{need.width}") \
+            + (f"w{need.window}" if need.window else "")
         groups.append(PageGroup(name=name, cache_ids=tuple(cids), window=need.window, num_blocks=n_blocks))
         kinds.append(need)
     return groups, kinds
@@ -63,6 +73,13 @@ class CacheStorage:
         self.states: Dict[int, torch.Tensor] = {}
         self.bytes = 0
         for g, (grp, need) in enumerate(zip(groups, kinds)):
+            if isinstance(need, RowNeed):
+                t = torch.zeros((len(grp.cache_ids), grp.num_blocks, block_size, need.width), dtype=dtype, device=device)
+                self.kv.append(t)
+                self.bytes += t.numel() * t.element_size()
+                for i, cid in enumerate(grp.cache_ids):
+                    self._views[cid] = RowView(group=g, rows=t[i])
+                continue
             t = torch.zeros((len(grp.cache_ids), 2, grp.num_blocks, need.num_kv_heads, block_size, need.head_dim),
                             dtype=dtype, device=device)
             self.kv.append(t)

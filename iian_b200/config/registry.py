@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``config.json``'s ``architectures[0]``) to the
+"""One registry from an architecture's name (``config.json``'s ``architectures[0]``, or its ``architecture``) to the
 plug-in that knows it.
 
 Mirrors the reference's ``ArchRegistry`` / ``IIAN_REGISTER_ARCH`` (include/iian/arch.h:36-52,
@@ -75,7 +75,7 @@ def get_architecture(name: str) -> Architecture:
 
 def _load_builtin() -> None:
     # importing the module registers the plug-in
-    from ..models import qwen3  # noqa: F401
+    from ..models import galodra, qwen3  # noqa: F401
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
@@ -90,9 +90,13 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
+    """The plug-in a ``config.json`` names: the first entry of ``architectures`` (a list of names), or ``architecture``
+    (one name)."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ValueError("config.json: 'architectures' must be a non-empty list of names")
+        raise ValueError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     return get_architecture(archs[0])
 
 

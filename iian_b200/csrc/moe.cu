@@ -1,0 +1,251 @@
+// Routed experts: router scores, the plan of a step (which rows go to which expert), the gather that scales each
+// expert's input by the router's weight, grouped matrix products over the rows sorted by expert, and the sum of a
+// token's expert outputs.
+//
+//   s = sigmoid(z) (z: router logits, float32);  a token takes the `top` experts with the largest s (ties: lowest
+//   index); its weight for expert e is s_e, not renormalised, and multiplies the expert's INPUT:
+//       y = sum over chosen e of  Wdown_e (act(Wgate_e (s_e h)) * (Wup_e (s_e h)))
+//
+// Nothing here needs the host to know how many rows an expert got: the plan lives in device memory and the grouped
+// product is launched for an upper bound of row tiles (tiles beyond the plan's count return at once), so the whole
+// feed-forward can be recorded into a CUDA graph.  Every output element adds its products in the order k = 0, 1, ...,
+// and a token's expert outputs are added in the order of its choices, so a row's result does not depend on the batch.
+#include "common.cuh"
+
+namespace iian {
+
+constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
+
+// One warp per token.  ids / wts: [N, top].
+__global__ void moe_route_kernel(const float * __restrict__ logits, long long ld, int E, int top, int * __restrict__ ids,
+                                 float * __restrict__ wts, int N) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long) blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= N) return;
+    const float * z = logits + t * ld;
+    unsigned long long taken_lo = 0;          // experts already chosen, for the lanes' own candidates (by slot i / 32)
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane, i = 0; e < E; e += 32, i++) {
+            if (i < 64 && ((taken_lo >> i) & 1ull)) continue;
+            const float v = z[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (best_e != 0x7fffffff && (best_e & 31) == lane) taken_lo |= 1ull << (best_e >> 5);
+        if (lane == 0) {
+            ids[t * top + k] = best_e == 0x7fffffff ? 0 : best_e;
+            wts[t * top + k] = best_e == 0x7fffffff ? 0.0f : 1.0f / (1.0f + expf(-best));
+        }
+    }
+}
+
+// One block.  offsets: [E + 1] first sorted row of each expert; pos: [M] sorted row of each (token, choice);
+// tiles: [2 * max_tiles + 1]: n_tiles, then (expert, first row) per row tile of kTileM rows.
+__global__ void moe_plan_kernel(const int * __restrict__ ids, int M, int E, int * __restrict__ offsets, int * __restrict__ pos,
+                                int * __restrict__ tiles, int max_tiles) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ int sm[];               // counts [E], cursor [E]
+    int * counts = sm;
+    int * cursor = sm + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < M; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = run;
+            cursor[e] = run;
+            for (int r = 0; r < counts[e] && nt < max_tiles; r += kTileM) {
+                tiles[1 + 2 * nt] = e;
+                tiles[2 + 2 * nt] = run + r;
+                nt++;
+            }
+            run += counts[e];
+        }
+        offsets[E] = run;
+        tiles[0] = nt;
+    }
+    __syncthreads();
+    // the order of an expert's rows among themselves is left to the atomics: a row's arithmetic does not depend on it
+    for (int i = threadIdx.x; i < M; i += blockDim.x) pos[i] = atomicAdd(&cursor[ids[i]], 1);
+}
+
+// xs[pos[t * top + k], :] = A(w[t, k] * h[t, :]);  rows[pos] = t * top + k
+template <typename A>
+__global__ void moe_scatter_kernel(const A * __restrict__ h, const int * __restrict__ pos, const float * __restrict__ wts,
+                                   A * __restrict__ xs, int W, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = blockIdx.x;              // (token, choice)
+    const size_t t = i / top;
+    const float w = wts[i];
+    const A * src = h + t * W;
+    A * dst = xs + (size_t) pos[i] * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = from_f32<A>(w * to_f32(src[c]));
+}
+
+// out[t, :] = sum_k ys[pos[t * top + k], :]  (k ascending)
+template <typename A>
+__global__ void moe_combine_kernel(const A * __restrict__ ys, const int * __restrict__ pos, A * __restrict__ out, int W, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int k = 0; k < top; k++) acc += to_f32(ys[(size_t) pos[t * top + k] * W + c]);
+        out[t * W + c] = from_f32<A>(acc);
+    }
+}
+
+__device__ __forceinline__ float moe_act(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    const float t = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.0f + tanhf(t));
+}
+
+// Rows [r0, r0 + rows) of x (sorted by expert) times expert e's weight block w[e] ([n_out, K], row-major):
+// out[r, m] = sum_k x[r, k] * w[e][m, k];  with GATED, w2[e] is a second block of the same shape and
+// out[r, m] = act(x . w[e][m]) * (x . w2[e][m]).
+template <typename A, typename WT, bool GATED>
+__global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restrict__ x, const WT * __restrict__ w,
+                                                               const WT * __restrict__ w2, A * __restrict__ out,
+                                                               const int * __restrict__ offsets, const int * __restrict__ tiles,
+                                                               int n_out, int K, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if ((int) blockIdx.y >= tiles[0]) return;
+    const int e = tiles[1 + 2 * blockIdx.y], r0 = tiles[2 + 2 * blockIdx.y];
+    const int r_end = min(offsets[e + 1], r0 + kTileM);
+    __shared__ float xs[kTileK][kTileM + 4];
+    __shared__ float ws[kTileK][kTileN + 4];
+    __shared__ float w2s[GATED ? kTileK : 1][kTileN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * kTileN;
+    const int tx = tid % 16, ty = tid / 16;
+    const int lrow = tid / 4, lk = (tid % 4) * 4;
+    const WT * we = w + (size_t) e * n_out * K;
+    const WT * w2e = GATED ? w2 + (size_t) e * n_out * K : nullptr;
+    float acc[4][4], acc2[GATED ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            acc[i][j] = 0.0f;
+            if (GATED) acc2[i][j] = 0.0f;
+        }
+    for (int k0 = 0; k0 < K; k0 += kTileK) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int k = k0 + lk + q;
+            const int r = r0 + lrow, m = m0 + lrow;
+            xs[lk + q][lrow] = (r < r_end && k < K) ? to_f32(x[(size_t) r * K + k]) : 0.0f;
+            ws[lk + q][lrow] = (m < n_out && k < K) ? to_f32(we[(size_t) m * K + k]) : 0.0f;
+            if (GATED) w2s[lk + q][lrow] = (m < n_out && k < K) ? to_f32(w2e[(size_t) m * K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kTileK; k++) {
+            float a[4], b[4], b2[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                b[j] = ws[k][tx * 4 + j];
+                if (GATED) b2[j] = w2s[k][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if (GATED) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = r0 + ty * 4 + i;
+        if (r >= r_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int m = m0 + tx * 4 + j;
+            if (m >= n_out) continue;
+            float v = acc[i][j];
+            // the gate and up products are rounded to the activation type first, as separate products would leave them
+            if (GATED) v = moe_act(to_f32(from_f32<A>(v)), act) * to_f32(from_f32<A>(acc2[i][j]));
+            out[(size_t) r * n_out + m] = from_f32<A>(v);
+        }
+    }
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+IIAN_API int iian_moe_tile_rows() { return kTileM; }
+
+// logits f32 (row stride ld) -> ids i32 [N, top], wts f32 [N, top]
+IIAN_API int iian_moe_route(const float * logits, long long ld, int E, int top, int * ids, float * wts, int N, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (E <= 0 || top <= 0 || top > E || E > 2048) return IIAN_ERR_SHAPE;
+    const int warps = 4;
+    return iian_launch(moe_route_kernel, dim3((N + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, ld, E, top, ids, wts, N);
+}
+
+// ids [M] -> offsets [E + 1], pos [M], tiles [1 + 2 * max_tiles]
+IIAN_API int iian_moe_plan(const int * ids, int M, int E, int * offsets, int * pos, int * tiles, int max_tiles, cudaStream_t stream) {
+    if (M <= 0) return IIAN_OK;
+    if (E <= 0 || E > 2048 || max_tiles < (M + kTileM - 1) / kTileM + E) return IIAN_ERR_SHAPE;
+    return iian_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t) 2 * E * sizeof(int), stream, ids, M, E, offsets, pos, tiles, max_tiles);
+}
+
+IIAN_API int iian_moe_scatter(const void * h, const int * pos, const float * wts, void * xs, int act_dtype, int N, int W, int top,
+                              cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    const int threads = W >= 1024 ? 256 : 128;
+    const unsigned blocks = (unsigned) ((size_t) N * top);
+    if (act_dtype == IIAN_F32) return iian_launch(moe_scatter_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) h, pos, wts, (float *) xs, W, top);
+    if (act_dtype == IIAN_BF16) return iian_launch(moe_scatter_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) h, pos, wts, (__nv_bfloat16 *) xs, W, top);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_moe_combine(const void * ys, const int * pos, void * out, int act_dtype, int N, int W, int top, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    const int threads = W >= 1024 ? 256 : 128;
+    if (act_dtype == IIAN_F32) return iian_launch(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) ys, pos, (float *) out, W, top);
+    if (act_dtype == IIAN_BF16) return iian_launch(moe_combine_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) ys, pos, (__nv_bfloat16 *) out, W, top);
+    return IIAN_ERR_DTYPE;
+}
+
+// x [M, K] sorted by expert; w (and w2, for the gated form) [E, n_out, K]; out [M, n_out]; act: 0 silu, 1 gelu (tanh)
+IIAN_API int iian_moe_grouped_gemm(const void * x, const void * w, const void * w2, void * out, const int * offsets, const int * tiles,
+                                   int max_tiles, int act_dtype, int w_dtype, int n_out, int K, int act, cudaStream_t stream) {
+    if (max_tiles <= 0 || n_out <= 0) return IIAN_OK;
+    if (K <= 0 || max_tiles > 65535) return IIAN_ERR_SHAPE;
+    dim3 grid((n_out + kTileN - 1) / kTileN, max_tiles);
+    typedef __nv_bfloat16 bf;
+#define IIAN_MOE(AT, WT)                                                                                                     \
+    do {                                                                                                                     \
+        if (w2 != nullptr)                                                                                                   \
+            return iian_launch(moe_grouped_gemm_kernel<AT, WT, true>, grid, dim3(256), 0, stream, (const AT *) x, (const WT *) w, \
+                               (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act);                                  \
+        return iian_launch(moe_grouped_gemm_kernel<AT, WT, false>, grid, dim3(256), 0, stream, (const AT *) x, (const WT *) w, \
+                           (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act);                                      \
+    } while (0)
+    if (act_dtype == IIAN_F32 && w_dtype == IIAN_F32) IIAN_MOE(float, float);
+    if (act_dtype == IIAN_BF16 && w_dtype == IIAN_BF16) IIAN_MOE(bf, bf);
+#undef IIAN_MOE
+    return IIAN_ERR_DTYPE;
+}

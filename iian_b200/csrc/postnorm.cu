@@ -1,0 +1,160 @@
+// Row-wise kernels of post-norm layers: the gated residual sum with its LayerNorm, a weighted sum of several
+// streams (depth mix), and the gated activation of a feed-forward with a choice of activation.
+//
+// The stream is float32; `A` is the activation type (float in the 32-bit path, bfloat16 in the serving path).
+// Every row is reduced in an order fixed by the row length alone, so a row's result does not depend on the batch.
+//
+//   gated_add_layer_norm:  s = alpha * x + sub * sigmoid(g + gb);   y = (s - mean(s)) / sqrt(var(s) + eps) * w + b
+//                          with var the mean of the squared deviations (two passes over the row, held in shared memory)
+//   depth_mix:             y[r] = sum_j c[j] * X_j[row_j(r)]   in the order j = 0, 1, 2, ...
+//   gated_act:             y = act(gate) * up,  act = silu (z / (1 + exp(-z))) or the tanh form of gelu
+//                          (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))
+#include "common.cuh"
+
+namespace iian {
+
+constexpr int kMaxMixTerms = 128;
+struct MixTerms {
+    const float * x[kMaxMixTerms];
+};
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+template <typename A, typename G>
+__global__ void gated_add_layer_norm_kernel(const float * __restrict__ x, const A * __restrict__ sub, long long ld_sub,
+                                            const G * __restrict__ glogit, long long ld_g, const float * __restrict__ gbias,
+                                            const float * __restrict__ w, const float * __restrict__ b,
+                                            float * __restrict__ out, A * __restrict__ out_act,
+                                            int H, float alpha, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    const float * xr = x + n * H;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = alpha * xr[i];
+        if (sub != nullptr) {
+            float s = to_f32(sub[n * ld_sub + i]);
+            if (glogit != nullptr) s *= sigmoid_f(to_f32(glogit[n * ld_g + i]) + (gbias != nullptr ? gbias[i] : 0.0f));
+            v += s;
+        }
+        row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float) H;
+    float dev = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = row[i] - mean;
+        dev += d * d;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(dev, scratch) / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float y = (row[i] - mean) * inv * w[i] + (b != nullptr ? b[i] : 0.0f);
+        if (out != nullptr) out[n * H + i] = y;
+        if (out_act != nullptr) out_act[n * H + i] = from_f32<A>(y);
+    }
+}
+
+template <typename A>
+__global__ void depth_mix_kernel(MixTerms terms, int n_terms, const float * __restrict__ coef, const int * __restrict__ rows,
+                                 int n_src, int last_is_selected, float * __restrict__ out, A * __restrict__ out_act, int H) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t r = blockIdx.x;
+    long long src = (long long) r;
+    if (rows != nullptr) src = rows[r];
+    const bool src_ok = src >= 0 && src < n_src;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < n_terms; j++) {
+            const bool own = rows == nullptr || (last_is_selected && j == n_terms - 1);
+            float v = 0.0f;
+            if (own) v = terms.x[j][r * H + i];
+            else if (src_ok) v = terms.x[j][(size_t) src * H + i];
+            acc = fmaf(coef[j], v, acc);
+        }
+        if (out != nullptr) out[r * H + i] = acc;
+        if (out_act != nullptr) out_act[r * H + i] = from_f32<A>(acc);
+    }
+}
+
+__device__ __forceinline__ float act_apply(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));
+    const float t = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.0f + tanhf(t));
+}
+
+// in rows: [gate (F) | up (F)] (interleave 0) or groups of 16 columns holding 8 gate values and then the 8 up
+// values of the same features (interleave 8); row stride ld_in elements
+template <typename A>
+__global__ void gated_act_kernel(const A * __restrict__ in, long long ld_in, A * __restrict__ out, int F, size_t total,
+                                 int interleave, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t r = idx / F;
+    const int col = (int) (idx - r * F);
+    const size_t gi = r * ld_in + (interleave ? (size_t) (col / 8) * 16 + col % 8 : (size_t) col);
+    const size_t ui = interleave ? gi + 8 : gi + F;
+    out[idx] = from_f32<A>(act_apply(to_f32(in[gi]), act) * to_f32(in[ui]));
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+static int norm_threads(int H) { return H >= 2048 ? 512 : H >= 512 ? 256 : 128; }
+
+// x f32 [N, H]; sub (act dtype, row stride ld_sub) or null; glogit (gate dtype, row stride ld_g) or null; gbias f32 [H] or
+// null; w f32 [H]; b f32 [H] or null; out f32 [N, H] or null; out_act (act dtype) [N, H] or null
+IIAN_API int iian_gated_add_layer_norm(const float * x, const void * sub, long long ld_sub, const void * glogit, long long ld_g,
+                                       int gate_dtype, const float * gbias, const float * w, const float * b, float * out,
+                                       void * out_act, int act_dtype, int N, int H, float alpha, float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0 || (size_t) H * 4 > 200 * 1024) return IIAN_ERR_LIMIT;
+    const size_t smem = (size_t) H * 4;
+    const int threads = norm_threads(H);
+    typedef __nv_bfloat16 bf;
+#define IIAN_GLN(AT, GT)                                                                                                     \
+    do {                                                                                                                     \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_add_layer_norm_kernel<AT, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+        return iian_launch(gated_add_layer_norm_kernel<AT, GT>, dim3(N), dim3(threads), smem, stream, x, (const AT *) sub, ld_sub, \
+                           (const GT *) glogit, ld_g, gbias, w, b, out, (AT *) out_act, H, alpha, eps);                      \
+    } while (0)
+    if (act_dtype == IIAN_F32 && gate_dtype == IIAN_F32) IIAN_GLN(float, float);
+    if (act_dtype == IIAN_BF16 && gate_dtype == IIAN_BF16) IIAN_GLN(bf, bf);
+    if (act_dtype == IIAN_BF16 && gate_dtype == IIAN_F32) IIAN_GLN(bf, float);
+#undef IIAN_GLN
+    return IIAN_ERR_DTYPE;
+}
+
+// terms: n_terms pointers to f32 [*, H]; coef f32 [n_terms]; rows (i32 [R]) or null: term j < n_terms - 1 (all terms
+// unless last_is_selected) is read at row rows[r], the last one at row r
+IIAN_API int iian_depth_mix(const float * const * terms, int n_terms, const float * coef, const int * rows, int n_src,
+                            int last_is_selected, float * out, void * out_act, int act_dtype, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return IIAN_OK;
+    if (n_terms <= 0 || n_terms > kMaxMixTerms) return IIAN_ERR_LIMIT;
+    MixTerms t;
+    for (int j = 0; j < kMaxMixTerms; j++) t.x[j] = j < n_terms ? terms[j] : nullptr;
+    const int threads = norm_threads(H);
+    if (act_dtype == IIAN_F32) return iian_launch(depth_mix_kernel<float>, dim3(R), dim3(threads), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (float *) out_act, H);
+    if (act_dtype == IIAN_BF16) return iian_launch(depth_mix_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (__nv_bfloat16 *) out_act, H);
+    return IIAN_ERR_DTYPE;
+}
+
+// act: 0 silu, 1 gelu (tanh form)
+IIAN_API int iian_gated_act(const void * in, long long ld_in, void * out, int act_dtype, int N, int F, int interleave, int act,
+                            cudaStream_t stream) {
+    if (interleave != 0 && (interleave != 8 || F % 8 != 0)) return IIAN_ERR_SHAPE;
+    if (act != 0 && act != 1) return IIAN_ERR_SHAPE;
+    const size_t total = (size_t) N * F;
+    if (total == 0) return IIAN_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    if (act_dtype == IIAN_F32) return iian_launch(gated_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) in, ld_in, (float *) out, F, total, interleave, act);
+    if (act_dtype == IIAN_BF16) return iian_launch(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) in, ld_in, (__nv_bfloat16 *) out, F, total, interleave, act);
+    return IIAN_ERR_DTYPE;
+}

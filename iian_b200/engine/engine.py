@@ -22,7 +22,7 @@ import torch
 
 from .. import ops
 from ..config.engine import EngineConfig
-from ..parts.base import KVNeed
+from ..parts.base import entry_elements, is_paged
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, request_seed
 from .model import Model
@@ -89,7 +89,7 @@ class Engine:
         if tokens < self.max_model_len:
             raise ValueError(f"the KV cache holds {tokens} tokens, less than max_model_len {self.max_model_len}; "
                              f"lower --max-model-len or raise --kv-cache-tokens / --kv-cache-gb")
-        windows = [n.window for n in model.cache_needs().values() if isinstance(n, KVNeed) and n.window]
+        windows = [n.window for n in model.cache_needs().values() if is_paged(n) and n.window]
         window_cap = None
         if windows:
             window_cap = c.sched.max_num_seqs * (max(windows) + c.sched.max_num_batched_tokens + 2 * bs)
@@ -116,8 +116,7 @@ class Engine:
 
     def _cache_bytes_per_token(self) -> int:
         esize = 2 if self.model.dtype == torch.bfloat16 else 4
-        return sum(2 * n.num_kv_heads * n.head_dim * esize for n in self.model.cache_needs().values()
-                   if isinstance(n, KVNeed))
+        return sum(entry_elements(n) * esize for n in self.model.cache_needs().values())
 
     # ---- submission ---------------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, priority: int = 0,

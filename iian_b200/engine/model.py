@@ -163,7 +163,12 @@ class Model:
             libs.update(part.kernel_libraries())
         if self.dtype == torch.bfloat16:
             from ..csrc import build
-            libs.update(build.BF16_SOURCES)
+            # what the bfloat16 path adds to a part's general kernels: the products' fast forms wherever a part multiplies
+            # matrices, the tensor-core attention kernels wherever a part attends over keys and values per head
+            if "gemm_simt" in libs:
+                libs.update(build.BF16_PRODUCT_SOURCES)
+            if "attention_generic" in libs:
+                libs.update(build.BF16_ATTENTION_SOURCES)
         return sorted(libs)
 
     # ---- one step ----------------------------------------------------------------------------

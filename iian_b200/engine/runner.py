@@ -25,7 +25,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager, RequestCache
 from ..cache.storage import CacheStorage, plan_groups
-from ..parts.base import KVNeed, StateNeed, prefix_reusable
+from ..parts.base import StateNeed, prefix_reusable
 from .model import Model
 
 

@@ -850,6 +850,196 @@ class CudaKernels:
                   _code(q, "q"), n, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
                   scale, window or 0, _stream()), "paged_attention_generic")
 
+    # ---- post-norm layers: gated residual sum + LayerNorm, depth mix, gated activation (csrc/postnorm.cu) ------------
+    @staticmethod
+    def _rows(t: Optional[torch.Tensor], what: str):
+        """(pointer, row stride) of a CUDA matrix whose rows are contiguous (a column slice of a wider matrix is fine)."""
+        if t is None:
+            return 0, 0
+        if not t.is_cuda:
+            raise KernelError(f"{what}: tensor is on {t.device}; the engine's kernels run on CUDA only")
+        if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+            raise KernelError(f"{what}: expected a matrix with contiguous rows")
+        return t.data_ptr(), t.stride(0)
+
+    def gated_add_layer_norm(self, x: torch.Tensor, sub: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                             gate_bias: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                             alpha: float, eps: float, out: Optional[torch.Tensor], out_act: Optional[torch.Tensor]) -> None:
+        """``y = LayerNorm(alpha * x + sub * sigmoid(gate + gate_bias)) * weight + bias``; ``out`` float32 and / or
+        ``out_act`` in the activation dtype.  ``sub`` and ``gate`` may be column slices; without ``sub`` it is the plain
+        norm of ``alpha * x``."""
+        n, h = x.shape
+        act = out_act if out_act is not None else sub
+        act_code = _code(act, "layer norm") if act is not None else F32
+        for t, what in ((sub, "sub"), (gate, "gate")):
+            if t is not None and t.shape != (n, h):
+                raise KernelError(f"gated_add_layer_norm: {what} {tuple(t.shape)} does not match x {tuple(x.shape)}")
+        if sub is not None and _code(sub, "sub") != act_code:
+            raise KernelError("gated_add_layer_norm: sub and out_act must share the activation dtype")
+        sp, ld_sub = self._rows(sub, "sub")
+        gp, ld_g = self._rows(gate, "gate")
+        fn = _fn("postnorm", "iian_gated_add_layer_norm",
+                 [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_float, c_float, c_void_p])
+        _check(fn(_cuda(x, "stream", torch.float32), sp, ld_sub, gp, ld_g, _code(gate, "gate") if gate is not None else act_code,
+                  _cuda(gate_bias, "gate bias", torch.float32), _cuda(weight, "norm weight", torch.float32),
+                  _cuda(bias, "norm bias", torch.float32), _cuda(out, "norm out", torch.float32), _cuda(out_act, "norm out"),
+                  act_code, n, h, alpha, eps, _stream()), "gated_add_layer_norm")
+
+    def depth_mix(self, terms, coef: torch.Tensor, rows: Optional[torch.Tensor], last_is_selected: bool,
+                  out: Optional[torch.Tensor], out_act: Optional[torch.Tensor]) -> None:
+        """``y[r] = sum_j coef[j] * terms[j][row_j(r)]``: float32 streams [*, H]; with ``rows`` every term (but the last, if
+        ``last_is_selected``) is read at ``rows[r]``."""
+        ref = out if out is not None else out_act
+        r, h = ref.shape
+        ptrs = (c_void_p * len(terms))(*[_cuda(t, "mix term", torch.float32) for t in terms])
+        if coef.numel() != len(terms) or any(t.shape[1] != h for t in terms):
+            raise KernelError("depth_mix: one coefficient per term, all terms of the output's width")
+        fn = _fn("postnorm", "iian_depth_mix", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                                c_int, c_int, c_void_p])
+        _check(fn(ptrs, len(terms), _cuda(coef, "mix coefficients", torch.float32), _cuda(rows, "rows", torch.int32),
+                  terms[0].shape[0], 1 if last_is_selected else 0, _cuda(out, "mix out", torch.float32), _cuda(out_act, "mix out"),
+                  _code(out_act, "mix out") if out_act is not None else F32, r, h, _stream()), "depth_mix")
+
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def gated_act(self, gate_up: torch.Tensor, out: torch.Tensor, interleave: int, activation: str) -> None:
+        """``out = act(gate) * up`` for rows ``[gate | up]`` (or interleaved in groups of 8); ``gate_up`` may be a column slice."""
+        n, f2 = gate_up.shape
+        if out.shape != (n, f2 // 2) or f2 % 2 or out.dtype != gate_up.dtype:
+            raise KernelError("gated_act: out must be [N, F] for gate_up [N, 2F] of the same dtype")
+        gp, ld = self._rows(gate_up, "gate_up")
+        fn = _fn("postnorm", "iian_gated_act", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(gp, ld, _cuda(out, "gated_act out"), _code(out, "gated_act out"), n, f2 // 2, interleave,
+                  self.ACTIVATIONS[activation], _stream()), "gated_act")
+
+    # ---- attention over a cached latent (csrc/latent_attention.cu) ------------------------------------------------
+    def latent_prep(self, qd: torch.Tensor, q_off: int, dkv_off: int, cache_rows: Optional[torch.Tensor], q_cat: torch.Tensor,
+                    norm_weight: torch.Tensor, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                    slots: Optional[torch.Tensor], *, num_heads: int, dim: int, rot: int, rank: int, rot_dims: int,
+                    eps: float) -> None:
+        """From the projected rows ``qd`` (queries at column ``q_off``, the down-projected latent and shared key part at
+        ``dkv_off``): normalise the latent, rotate the key part, store both at the token's cache cell, and put the
+        rotated part of every query head behind the ``rank`` columns of its row of ``q_cat`` [N, H, rank + rot]."""
+        n = qd.shape[0]
+        width = rank + rot
+        if q_cat.shape != (n, num_heads, width) or q_cat.dtype != qd.dtype:
+            raise KernelError("latent_prep: q_cat must be [N, heads, rank + rot] in the activation dtype")
+        n_cells = 0
+        if cache_rows is not None:
+            if cache_rows.dtype != qd.dtype or cache_rows.shape[-1] != width:
+                raise KernelError(f"latent_prep: cache {tuple(cache_rows.shape)} {cache_rows.dtype} does not match")
+            n_cells = cache_rows.numel() // width
+        qp, ld = self._rows(qd, "projected rows")
+        fn = _fn("latent_attention", "iian_latent_prep",
+                 [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p])
+        _check(fn(qp, ld, q_off, dkv_off, _cuda(cache_rows, "latent cache"), _cuda(q_cat, "q_cat"),
+                  _cuda(norm_weight, "latent norm weight", torch.float32), _cuda(inv_freq, "inv_freq", torch.float32),
+                  _cuda(positions, "positions", torch.int32), _cuda(slots if cache_rows is not None else None, "slots", torch.int32),
+                  _code(qd, "projected rows"), n, num_heads, dim, rot, rank, rot_dims if inv_freq is not None else 0, eps,
+                  n_cells, _stream()), "latent_prep")
+
+    def head_linear(self, inp: torch.Tensor, in_off: int, in_head_stride: int, w: torch.Tensor, w_head_stride: int, w_in_stride: int,
+                    w_out_stride: int, out: torch.Tensor, out_off: int, out_head_stride: int, *, num_heads: int, n_in: int,
+                    n_out: int) -> None:
+        """Per token and head: ``out[t, h, j] = sum_i inp[t, h, i] * w[h * w_head_stride + i * w_in_stride + j * w_out_stride]``;
+        ``inp`` / ``out`` are matrices whose row holds the heads at ``*_off + h * *_head_stride``."""
+        n = inp.shape[0]
+        ip, ld_in = self._rows(inp, "head_linear in")
+        op, ld_out = self._rows(out, "head_linear out")
+        es = inp.element_size()
+        fn = _fn("latent_attention", "iian_head_linear",
+                 [c_void_p, c_longlong, c_int, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_void_p])
+        if out.dtype != inp.dtype:
+            raise KernelError("head_linear: in and out must share the activation dtype")
+        _check(fn(ip + in_off * es, ld_in, in_head_stride, _cuda(w, "head_linear w"), _code(w, "head_linear w"), w_head_stride,
+                  w_in_stride, w_out_stride, op + out_off * es, ld_out, out_head_stride, _code(inp, "head_linear in"), n,
+                  num_heads, n_in, n_out, _stream()), "head_linear")
+
+    def latent_attention(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, out: torch.Tensor, sink: Optional[torch.Tensor],
+                         meta, *, num_heads: int, rank: int, scale: float, window: Optional[int]) -> None:
+        """``q_cat`` [N, H, width], ``cache_rows`` [pages, page_size, width] -> ``out`` [N, H, rank]: softmax (with the
+        sink in the denominator) over the visible cached rows, weighted sum of their first ``rank`` columns."""
+        n, h, width = q_cat.shape
+        if h != num_heads or cache_rows.shape[-1] != width or out.shape != (n, h, rank) or cache_rows.dtype != q_cat.dtype \
+                or out.dtype != q_cat.dtype:
+            raise KernelError(f"latent_attention: q {tuple(q_cat.shape)}, cache {tuple(cache_rows.shape)}, out {tuple(out.shape)} do not fit")
+        bt = meta.block_table
+        fn = _fn("latent_attention", "iian_latent_attention",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+        _check(fn(_cuda(q_cat, "q_cat"), _cuda(cache_rows, "latent cache"), _cuda(out, "attention out"),
+                  _cuda(sink, "sink", torch.float32), _cuda(meta.positions, "positions", torch.int32),
+                  _cuda(meta.seq_of_token, "seq_of_token", torch.int32), _cuda(bt, "block table", torch.int32), bt.shape[1],
+                  _cuda(meta.ctx_len, "ctx_len", torch.int32), _code(q_cat, "q_cat"), n, h, rank, width, cache_rows.shape[1],
+                  cache_rows.shape[0], scale, window or 0, _stream()), "latent_attention")
+
+    # ---- routed experts (csrc/moe.cu) -----------------------------------------------------------------------------
+    _moe_tile_rows = None
+
+    def moe_tile_rows(self) -> int:
+        if CudaKernels._moe_tile_rows is None:
+            lib = _build.load("moe")
+            lib.iian_moe_tile_rows.restype = c_int
+            CudaKernels._moe_tile_rows = int(lib.iian_moe_tile_rows())
+        return CudaKernels._moe_tile_rows
+
+    def moe_max_tiles(self, n_rows: int, num_experts: int) -> int:
+        """Upper bound of the row tiles of a grouped product over ``n_rows`` rows sorted by expert."""
+        return -(-n_rows // self.moe_tile_rows()) + num_experts
+
+    def moe_route(self, logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+        """Router logits (float32, may be a column slice) -> the ``top`` experts of each token by sigmoid score, and the scores."""
+        n, e = logits.shape
+        if logits.dtype != torch.float32 or ids.shape != (n, top) or weights.shape != (n, top):
+            raise KernelError("moe_route: logits float32 [N, E]; ids / weights [N, top]")
+        lp, ld = self._rows(logits, "router logits")
+        fn = _fn("moe", "iian_moe_route", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+        _check(fn(lp, ld, e, top, _cuda(ids, "expert ids", torch.int32), _cuda(weights, "expert weights", torch.float32), n,
+                  _stream()), "moe_route")
+
+    def moe_plan(self, ids: torch.Tensor, num_experts: int, offsets: torch.Tensor, pos: torch.Tensor, tiles: torch.Tensor) -> None:
+        m = ids.numel()
+        max_tiles = (tiles.numel() - 1) // 2
+        if offsets.numel() != num_experts + 1 or pos.numel() != m:
+            raise KernelError("moe_plan: offsets [E + 1], pos [M]")
+        fn = _fn("moe", "iian_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+        _check(fn(_cuda(ids, "expert ids", torch.int32), m, num_experts, _cuda(offsets, "offsets", torch.int32),
+                  _cuda(pos, "pos", torch.int32), _cuda(tiles, "tiles", torch.int32), max_tiles, _stream()), "moe_plan")
+
+    def moe_scatter(self, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, xs: torch.Tensor, top: int) -> None:
+        n, w = h.shape
+        if xs.shape != (n * top, w) or xs.dtype != h.dtype:
+            raise KernelError("moe_scatter: xs must be [N * top, W] in the dtype of h")
+        fn = _fn("moe", "iian_moe_scatter", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(h, "moe in"), _cuda(pos, "pos", torch.int32), _cuda(weights, "expert weights", torch.float32),
+                  _cuda(xs, "moe rows"), _code(h, "moe in"), n, w, top, _stream()), "moe_scatter")
+
+    def moe_grouped_gemm(self, x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], out: torch.Tensor,
+                         offsets: torch.Tensor, tiles: torch.Tensor, activation: str = "silu") -> None:
+        """Rows of ``x`` sorted by expert times that expert's block of ``w`` [E, n_out, K]; with ``w2`` the gated form
+        ``act(x . w) * (x . w2)``."""
+        m, k = x.shape
+        n_out = w.shape[1]
+        if w.shape[2] != k or out.shape != (m, n_out) or (w2 is not None and w2.shape != w.shape) or out.dtype != x.dtype:
+            raise KernelError(f"moe_grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        fn = _fn("moe", "iian_moe_grouped_gemm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "moe rows"), _cuda(w, "expert weights"), _cuda(w2, "expert weights"), _cuda(out, "moe out"),
+                  _cuda(offsets, "offsets", torch.int32), _cuda(tiles, "tiles", torch.int32), (tiles.numel() - 1) // 2,
+                  _code(x, "moe rows"), _code(w, "expert weights"), n_out, k, self.ACTIVATIONS[activation], _stream()),
+               "moe_grouped_gemm")
+
+    def moe_combine(self, ys: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, top: int) -> None:
+        n, w = out.shape
+        if ys.shape != (n * top, w) or ys.dtype != out.dtype:
+            raise KernelError("moe_combine: ys must be [N * top, W] in the dtype of out")
+        fn = _fn("moe", "iian_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(ys, "moe out rows"), _cuda(pos, "pos", torch.int32), _cuda(out, "moe out"), _code(out, "moe out"), n, w, top,
+                  _stream()), "moe_combine")
+
     # ---- sampling ------------------------------------------------------------------------
     def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
         r, v = logits.shape

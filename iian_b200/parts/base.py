@@ -18,8 +18,8 @@ Interfaces
     the activation dtype.
 ``Mixer.forward(x, ctx, cache, writes_cache) -> y``
     ``x``: normalised rows ``[N, H]``; ``cache``: what :meth:`Mixer.cache_need` asked for (a
-    :class:`~iian_b200.cache.storage.KVView`, a :class:`~iian_b200.cache.storage.StateView` or
-    None); ``writes_cache`` is False when the run order lets this call read another call's cache.
+    :class:`~iian_b200.cache.storage.KVView`, a :class:`~iian_b200.cache.storage.RowView`, a
+    :class:`~iian_b200.cache.storage.StateView` or None); ``writes_cache`` is False when the run order lets this call read another call's cache.
     Returns ``[N, H]`` in the activation dtype.
 ``FeedForward.forward(x, ctx) -> y``
     rows in, rows out, ``[N, H]``.
@@ -63,6 +63,29 @@ class KVNeed:
 
 
 @dataclass(frozen=True)
+class RowNeed:
+    """Per-token entries of ONE row of ``width`` numbers that every head reads (a compressed latent with the
+    shared rotated key part behind it); ``window`` as for :class:`KVNeed`."""
+
+    width: int
+    window: Optional[int] = None
+
+
+def is_paged(need) -> bool:
+    """Whether the need is per-token entries kept in pages (as opposed to a fixed-size state, or nothing)."""
+    return isinstance(need, (KVNeed, RowNeed))
+
+
+def entry_elements(need) -> int:
+    """Numbers a paged need stores per token."""
+    if isinstance(need, KVNeed):
+        return 2 * need.num_kv_heads * need.head_dim
+    if isinstance(need, RowNeed):
+        return need.width
+    return 0
+
+
+@dataclass(frozen=True)
 class StateNeed:
     """A fixed-size state per request: one tensor of ``shape`` and ``dtype`` per slot.
 
@@ -77,7 +100,7 @@ class StateNeed:
 def prefix_reusable(need) -> bool:
     """Whether a request may skip tokens whose cache entries another request left behind.  Keys and values
     per token can be shared page by page; a fixed-size state cannot (it would need a snapshot per page)."""
-    return isinstance(need, KVNeed)
+    return is_paged(need)
 
 
 class Part:

@@ -93,3 +93,192 @@ class PreNormResidualBlock:
             request = self._norm_out(next_norm, next_consumer, residual, residual.shape[0], "feed_forward")
         d = self.feed_forward.forward(h2, ctx, norm_out=request) if request is not None else self.feed_forward.forward(h2, ctx)
         return residual, d
+
+
+class SigmoidGate:
+    """A gate of a sub-layer's output: ``sigmoid(W h + b)`` per element, ``h`` the sub-layer's input.  params: ``size``.
+    The matrix rides as extra rows in the sub-layer's own first product (``stack_rows``); the bias and the sigmoid are
+    applied by the kernel that adds the sub-layer's output to the stream."""
+
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.size = int(spec["size"])
+        self.weight = self.bias = None
+        self.graph_safe = True
+
+    def tensors(self):
+        from ..weights.loader import TensorSpec
+        return {"weight": TensorSpec((self.size, self.size)), "bias": TensorSpec((self.size,), init="zeros")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors["weight"]
+        self.bias = tensors["bias"].to(torch.float32).contiguous()
+
+    def kernel_libraries(self):
+        return ("postnorm",)
+
+
+class DepthMix:
+    """What a layer hands on is a learned mix of the embedding output and every layer result so far:
+    ``x = sum_j c[j] X_j``, ``j = 0 .. terms - 1``.  params: ``terms``."""
+
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.terms = int(spec["terms"])
+        self.coef = None
+        self.graph_safe = True
+
+    def tensors(self):
+        from ..weights.loader import TensorSpec
+        return {"weight": TensorSpec((self.terms,), init="ones_jitter")}
+
+    def bind(self, tensors) -> None:
+        self.coef = tensors["weight"].to(torch.float32).contiguous()
+
+    def kernel_libraries(self):
+        return ("postnorm",)
+
+
+@register_block("post_norm_residual")
+class PostNormResidualBlock:
+    """``y = norm1(alpha * x + g1(x) * mixer(x))``; ``z = norm2(alpha * y + g2(y) * ffn(y))``: the norm comes AFTER the sum,
+    the sub-layers read the stream itself, and the skip path is scaled by ``alpha``.
+
+    Slots: ``mixer``, ``mixer_norm`` (the norm after the mixer's sum), optionally ``feed_forward`` with
+    ``feed_forward_norm`` (a layer without feed-forward ends after the first norm); in ``extra``, all optional:
+    ``mixer_gate`` / ``feed_forward_gate`` (``sigmoid_gate``: the sub-layer's output is multiplied by
+    ``sigmoid(W h + b)`` of its input before the sum) and ``depth_mix`` (the stream handed to the next layer is a learned
+    mix of the embedding output and all layer results so far, ``terms`` of them).  ``extra`` also carries the constants
+    ``alpha`` as ``("alpha", PartSpec("constant", {"value": a}))``.
+
+    The norm kernel does the scaled skip, the gate's bias and sigmoid, the product with the sub-layer's output, the sum
+    and the LayerNorm in one pass, and leaves the float32 stream plus its copy in the activation dtype.  The stream
+    between layers is float32 in ``residual``; ``delta`` stays None (nothing is left to add)."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        if spec.slot("mixer") is None or spec.slot("mixer_norm") is None:
+            raise ValueError("arrangement post_norm_residual needs the slots mixer, mixer_norm")
+        if (spec.slot("feed_forward") is None) != (spec.slot("feed_forward_norm") is None):
+            raise ValueError("arrangement post_norm_residual: feed_forward and feed_forward_norm come together")
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device) if spec.feed_forward is not None else None
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "sum_norm"):
+                raise ValueError("arrangement post_norm_residual needs norms that fuse the sum (layer_norm)")
+        alpha = spec.slot("alpha")
+        self.alpha = float(alpha["value"]) if alpha is not None else 1.0
+        g1, g2, mix = spec.slot("mixer_gate"), spec.slot("feed_forward_gate"), spec.slot("depth_mix")
+        self.mixer_gate = SigmoidGate(g1, dtype, device) if g1 is not None else None
+        self.feed_forward_gate = SigmoidGate(g2, dtype, device) if g2 is not None and self.feed_forward is not None else None
+        self.depth_mix = DepthMix(mix, dtype, device) if mix is not None else None
+        self._stacked = False
+
+    def parts(self):
+        out = [("mixer", self.mixer), ("mixer_norm", self.mixer_norm)]
+        if self.feed_forward is not None:
+            out += [("feed_forward", self.feed_forward), ("feed_forward_norm", self.feed_forward_norm)]
+        for name in ("mixer_gate", "feed_forward_gate", "depth_mix"):
+            if getattr(self, name) is not None:
+                out.append((name, getattr(self, name)))
+        return tuple(out)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def _stack_gates(self) -> None:
+        """After the weights are bound: put each gate's matrix under its sub-layer's first product."""
+        for gate, part in ((self.mixer_gate, self.mixer), (self.feed_forward_gate, self.feed_forward)):
+            if gate is not None:
+                if not hasattr(part, "stack_rows"):
+                    raise ValueError(f"{type(part).__name__} cannot carry a gate's rows in its product")
+                part.stack_rows(gate.weight)
+                gate.weight = None
+        self._stacked = True
+
+    def forward(self, residual: torch.Tensor, delta, ctx, cache, writes_cache: bool, select_rows: Optional[torch.Tensor]):
+        if delta is not None:
+            raise RuntimeError("post_norm_residual: the layer before left something to add")
+        if not self._stacked:
+            self._stack_gates()
+        k = ops.kernels()
+        x = residual
+        history = None
+        if self.depth_mix is not None:
+            history = ctx.step_cache.setdefault("depth_history", [])
+            if not history:
+                history.append(x)            # X_0: what the embedding left
+        idx = len(history) if history is not None else 0
+        if x.dtype == self.dtype:
+            x_act = x
+        else:
+            x_act = ctx.step_cache.get("stream_act")
+            if x_act is None or x_act.shape != x.shape:
+                # the first layer reads what the embedding left (an exact copy of bfloat16 table rows)
+                x_act = ctx.buf("stream_act_in", x.shape, self.dtype)
+                k.depth_mix([x], _one(x.device), None, False, None, x_act)
+        # ---- mixer, gate, sum, norm ----
+        if self.mixer_gate is not None:
+            y_sub, g = self.mixer.forward(x_act, ctx, cache, writes_cache, with_extra=True)
+            gb = self.mixer_gate.bias
+        else:
+            y_sub, g, gb = self.mixer.forward(x_act, ctx, cache, writes_cache), None, None
+        last = self.feed_forward is None
+        name = f"result{idx}" if last else "mid"
+        y, y_act = self.mixer_norm.sum_norm(x, self.alpha, y_sub, g, gb, ctx, name, want_act=not last)
+        gathers = select_rows is not None and not getattr(ctx, "rows_identity", False)
+        if not last:
+            if gathers:          # the run order's last layer: only the wanted rows go through the feed-forward
+                r = select_rows.shape[0]
+                y_sel = ctx.buf("mid_rows", (r, y.shape[1]), y.dtype)
+                k.gather_rows(y, select_rows, y_sel)
+                if y_act is y:
+                    y_act_sel = y_sel
+                else:
+                    y_act_sel = ctx.buf("mid_act_rows", (r, y.shape[1]), y_act.dtype)
+                    k.gather_rows(y_act, select_rows, y_act_sel)
+                y, y_act = y_sel, y_act_sel
+            if self.feed_forward_gate is not None:
+                z_sub, g = self.feed_forward.forward(y_act, ctx, with_extra=True)
+                gb = self.feed_forward_gate.bias
+            else:
+                z_sub, g, gb = self.feed_forward.forward(y_act, ctx), None, None
+            z, _ = self.feed_forward_norm.sum_norm(y, self.alpha, z_sub, g, gb, ctx, f"result{idx}", want_act=False)
+            selected = gathers
+        else:
+            z = y
+            if gathers:
+                z_sel = ctx.buf("result_rows", (select_rows.shape[0], z.shape[1]), z.dtype)
+                k.gather_rows(z, select_rows, z_sel)
+                z = z_sel
+            selected = gathers
+        if self.depth_mix is None:
+            if z.dtype != self.dtype:
+                ctx.step_cache.pop("stream_act", None)
+            return z, None
+        # ---- the stream handed on: a mix of X_0 .. X_idx ----
+        terms = history + [z]
+        if len(terms) != self.depth_mix.terms:
+            raise RuntimeError(f"depth mix of {self.depth_mix.terms} terms after {len(terms) - 1} layers")
+        history.append(z)
+        out = ctx.buf(f"mixed{idx % 2}", z.shape, torch.float32)
+        if self.dtype == torch.float32:
+            k.depth_mix(terms, self.depth_mix.coef, select_rows if selected else None, selected, out, None)
+            return out, None
+        out_act = ctx.buf(f"mixed_act{idx % 2}", z.shape, self.dtype)
+        k.depth_mix(terms, self.depth_mix.coef, select_rows if selected else None, selected, out, out_act)
+        ctx.step_cache["stream_act"] = out_act
+        return out, None
+
+
+_ONES = {}
+
+
+def _one(device) -> torch.Tensor:
+    t = _ONES.get(device)
+    if t is None:
+        t = _ONES[device] = torch.ones(1, dtype=torch.float32, device=device)
+    return t

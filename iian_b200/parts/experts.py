@@ -1,0 +1,101 @@
+"""Routed experts: a feed-forward made of many small gated feed-forwards, of which each token uses a few.
+
+``z = Wrouter h`` in float32; scores ``s = sigmoid(z)``; a token takes the ``top`` experts with the largest scores and
+weighs them by those scores as they are (no renormalisation).  With ``weight_on = "input"`` the weight multiplies what
+the expert reads: ``y = sum_e expert_e(s_e h)``, ``expert(u) = Wdown (act(Wgate u) * (Wup u))``, no biases.
+
+The step never learns on the host how many rows an expert got.  A routing kernel picks experts, a one-block plan
+kernel sorts the (token, choice) rows by expert and lists the row tiles, the rows are gathered (and scaled), two
+grouped products run over the sorted rows -- gate and up with the activation in the epilogue, then down -- and a last
+kernel adds a token's expert outputs in the order of its choices.  All sizes are fixed by the number of tokens, so the
+part can be recorded into a CUDA graph.
+
+``stack_rows`` puts further rows that read the same input (a gate of the residual) under the router's, so that one
+product with float32 output serves both.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """params: ``hidden_size``, ``num_experts``, ``top``, ``intermediate_size`` (of one expert), ``activation``
+    (``silu`` | ``gelu_tanh``), ``score`` (``sigmoid``), ``weight_on`` (``input``)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.experts = int(p["num_experts"])
+        self.top = int(p["top"])
+        self.inter = int(p["intermediate_size"])
+        self.activation = p.get("activation", "silu")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"routed_experts: activation '{self.activation}' has no kernel")
+        if p.get("score", "sigmoid") != "sigmoid" or p.get("weight_on", "input") != "input":
+            raise ValueError("routed_experts: sigmoid scores that weigh the expert's input are what is built")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"routed_experts: top {self.top} of {self.experts} experts")
+        self.w_router = self.w_gate = self.w_up = self.w_down = None
+        self.extra_rows = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        t = {"router": TensorSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            t[f"e{e}.gate"] = TensorSpec((self.inter, self.hidden))
+            t[f"e{e}.up"] = TensorSpec((self.inter, self.hidden))
+            t[f"e{e}.down"] = TensorSpec((self.hidden, self.inter))
+        return t
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self._router = tensors["router"]
+        self.w_router = self._router.contiguous()
+        for name in ("gate", "up", "down"):
+            setattr(self, f"w_{name}", torch.stack([tensors[f"e{e}.{name}"] for e in range(self.experts)]).contiguous())
+
+    def stack_rows(self, rows: torch.Tensor) -> None:
+        self.extra_rows = rows
+        ws = [self._router, rows]
+        if ws[0].dtype != ws[1].dtype:
+            ws = [w.to(torch.float32) for w in ws]
+        self.w_router = torch.cat(ws, dim=0).contiguous()
+
+    def kernel_libraries(self):
+        return ("moe", "gemm_simt")
+
+    def forward(self, x, ctx, with_extra: bool = False):
+        k = ops.kernels()
+        n = x.shape[0]
+        top, E = self.top, self.experts
+        m = n * top
+        if n == 0:
+            out = ctx.buf("ffn_out", (0, self.hidden), self.dtype)
+            return (out, None) if with_extra else out
+        logits = ctx.buf("router_logits", (n, self.w_router.shape[0]), torch.float32)
+        k.linear(x, self.w_router, logits)
+        ids = ctx.buf("expert_ids", (n, top), torch.int32)
+        wts = ctx.buf("expert_weights", (n, top), torch.float32)
+        k.moe_route(logits[:, :E], top, ids, wts)
+        max_tiles = k.moe_max_tiles(m, E)
+        offsets = ctx.buf("expert_offsets", (E + 1,), torch.int32)
+        pos = ctx.buf("expert_pos", (m,), torch.int32)
+        tiles = ctx.buf("expert_tiles", (1 + 2 * max_tiles,), torch.int32)
+        k.moe_plan(ids, E, offsets, pos, tiles)
+        xs = ctx.buf("expert_in", (m, self.hidden), self.dtype)
+        k.moe_scatter(x, pos, wts, xs, top)
+        act = ctx.buf("expert_act", (m, self.inter), self.dtype)
+        k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation)
+        ys = ctx.buf("expert_out", (m, self.hidden), self.dtype)
+        k.moe_grouped_gemm(act, self.w_down, None, ys, offsets, tiles)
+        out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
+        k.moe_combine(ys, pos, out, top)
+        if with_extra:
+            return out, (logits[:, E:] if self.extra_rows is not None else None)
+        return out
