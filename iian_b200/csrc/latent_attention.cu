@@ -10,9 +10,9 @@
 //
 // Kernels:
 //   latent_prep      per token: RMS norm of the latent (float32 sums), rotation of the shared key part and of the
-//                    rotated part of every query head (angles from float64 products, so they are at least as exact
-//                    as 32-bit ones), write of the cache row, copy of the rotated query parts into the attention's
-//                    query rows
+//                    rotated part of every query head (frequencies and angles in float64, so they are at least as
+//                    exact as 32-bit ones at any position), write of the cache row, copy of the rotated query parts
+//                    into the attention's query rows
 //   head_linear      per token and head a small matrix product with that head's block of a stacked weight, in either
 //                    orientation (reduce over the weight's rows, or over its columns)
 //   latent_attention one warp per (token, head); keys in tiles of 32 that start at multiples of 32 of the ABSOLUTE key
@@ -30,7 +30,7 @@ constexpr int kLatMaxWidth = 1536;       // rank + rot
 template <typename A>
 __global__ void latent_prep_kernel(const A * __restrict__ qd, long long ld, int q_off, int dkv_off,
                                    A * __restrict__ cache, A * __restrict__ q_cat, const float * __restrict__ norm_w,
-                                   const float * __restrict__ inv_freq, const int * __restrict__ positions,
+                                   const double * __restrict__ inv_freq, const int * __restrict__ positions,
                                    const int * __restrict__ slots, int H, int dim, int rot, int rank, int rot_dims,
                                    float eps, long long n_cells) {
     pdl_wait();
@@ -42,7 +42,7 @@ __global__ void latent_prep_kernel(const A * __restrict__ qd, long long ld, int 
     const int half = rot_dims >> 1;
     const int p = positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const double a = (double) p * (double) inv_freq[i];
+        const double a = (double) p * inv_freq[i];
         double s, c;
         sincos(a, &s, &c);
         cs_sn[2 * i] = (float) c;
@@ -193,7 +193,7 @@ __global__ void latent_attention_kernel(const A * __restrict__ q, const A * __re
 using namespace iian;
 
 IIAN_API int iian_latent_prep(const void * qd, long long ld, int q_off, int dkv_off, void * cache, void * q_cat,
-                              const float * norm_w, const float * inv_freq, const int * positions, const int * slots,
+                              const float * norm_w, const double * inv_freq, const int * positions, const int * slots,
                               int act_dtype, int N, int H, int dim, int rot, int rank, int rot_dims, float eps,
                               long long n_cells, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;

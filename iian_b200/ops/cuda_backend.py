@@ -920,7 +920,8 @@ class CudaKernels:
                     eps: float) -> None:
         """From the projected rows ``qd`` (queries at column ``q_off``, the down-projected latent and shared key part at
         ``dkv_off``): normalise the latent, rotate the key part, store both at the token's cache cell, and put the
-        rotated part of every query head behind the ``rank`` columns of its row of ``q_cat`` [N, H, rank + rot]."""
+        rotated part of every query head behind the ``rank`` columns of its row of ``q_cat`` [N, H, rank + rot].
+        ``inv_freq`` is float64 [rot_dims / 2]."""
         n = qd.shape[0]
         width = rank + rot
         if q_cat.shape != (n, num_heads, width) or q_cat.dtype != qd.dtype:
@@ -935,7 +936,7 @@ class CudaKernels:
                  [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p])
         _check(fn(qp, ld, q_off, dkv_off, _cuda(cache_rows, "latent cache"), _cuda(q_cat, "q_cat"),
-                  _cuda(norm_weight, "latent norm weight", torch.float32), _cuda(inv_freq, "inv_freq", torch.float32),
+                  _cuda(norm_weight, "latent norm weight", torch.float32), _cuda(inv_freq, "inv_freq", torch.float64),
                   _cuda(positions, "positions", torch.int32), _cuda(slots if cache_rows is not None else None, "slots", torch.int32),
                   _code(qd, "projected rows"), n, num_heads, dim, rot, rank, rot_dims if inv_freq is not None else 0, eps,
                   n_cells, _stream()), "latent_prep")

@@ -114,7 +114,7 @@ class LatentAttention(Mixer):
         q_cat = ctx.buf("latent_q", (n, self.nh, self.width), self.dtype)
         # the latent's norm, the rotations, the cache write; rotated query parts go to the back of q_cat's rows
         k.latent_prep(qd, 0, self.q_size, cache.rows if writes_cache else None, q_cat, self.norm_w,
-                      pos.inv_freq, ctx.positions, meta.slots if writes_cache else None,
+                      pos.inv_freq64, ctx.positions, meta.slots if writes_cache else None,
                       num_heads=self.nh, dim=self.dim, rot=self.rot, rank=self.rank, rot_dims=pos.dim, eps=self.eps)
         # qa_g = Wuk_g^T q_g into the front of q_cat's rows
         k.head_linear(qd, 0, self.dim + self.rot, self.w_uk, self.dim * self.rank, self.rank, 1,

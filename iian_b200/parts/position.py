@@ -44,6 +44,7 @@ class Rotary(PositionEncoding):
         j = torch.arange(self.dim // 2, dtype=torch.float64)
         inv = scale * torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * j / self.dim)
         self.inv_freq = inv.to(torch.float32).to(device)
+        self.inv_freq64 = inv.to(device)         # for kernels that form the angle in float64
         self.key = ("rotary", self.dim, self.base, scale)
 
     def table(self, ctx):
@@ -69,3 +70,4 @@ class NoPosition(PositionEncoding):
     dim = 0
     style = 0
     inv_freq = None
+    inv_freq64 = None

@@ -92,9 +92,10 @@ def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str, m
     dkv = h @ w[pre + "dkv"].T
     c = rms_norm(dkv[:, :rank], w[pre + "dkv.norm"], eps)
     k_rot = dkv[:, rank:]
-    rdims, base = m["rot"]["dims"], m["rot"]["base"]
-    q_rot = rotate_half(q_rot, pos, rdims, base)
-    k_rot = rotate_half(k_rot, pos, rdims, base)
+    if m.get("rot"):                      # without it the "rotated" parts stay as projected
+        rdims, base = m["rot"]["dims"], m["rot"]["base"]
+        q_rot = rotate_half(q_rot, pos, rdims, base)
+        k_rot = rotate_half(k_rot, pos, rdims, base)
     k_plain = (c @ w[pre + "uk"].T).view(t, heads, dim)
     v = (c @ w[pre + "uv"].T).view(t, heads, vdim)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
