@@ -977,6 +977,49 @@ class CudaKernels:
                   _cuda(meta.ctx_len, "ctx_len", torch.int32), _code(q_cat, "q_cat"), n, h, rank, width, cache_rows.shape[1],
                   cache_rows.shape[0], scale, window or 0, _stream()), "latent_attention")
 
+    # the same on the tensor cores (csrc/latent_attention_mma.cu): bfloat16, rank 64 / 128 / 256 / 512, rot a multiple of 16
+    LATENT_MMA = os.environ.get("IIAN_LATENT_MMA", "1") not in ("0", "false", "off")
+
+    def latent_attention_mma_ok(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, rank: int) -> bool:
+        if not self.LATENT_MMA or q_cat.dtype != torch.bfloat16 or cache_rows.dtype != torch.bfloat16:
+            return False
+        fn = _fn("latent_attention_mma", "iian_latent_attention_mma_ok", [c_int, c_int, c_int])
+        return fn(rank, q_cat.shape[2], q_cat.shape[1]) == 0
+
+    def latent_attention_parts(self, num_seqs: int, max_q_len: int, num_heads: int, max_ctx: int, window: Optional[int]) -> int:
+        """Into how many parts the keys are cut so that a step with few rows still fills the GPU: a CTA takes 32
+        (token, head) rows of one sequence and holds most of an SM's shared memory at the widths of real models, so
+        the aim is one CTA per SM, each with at least two key tiles of 64."""
+        ctas = max(1, num_seqs * (-(-max_q_len * num_heads // 32)))
+        keys = min(max_ctx, window + max_q_len) if window else max_ctx
+        tiles = -(-keys // 64) + 1
+        return max(1, min(self.sm_count() // ctas, tiles // 2, 32))
+
+    def latent_attention_mma(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, out: torch.Tensor, sink: Optional[torch.Tensor],
+                             meta, *, num_heads: int, rank: int, scale: float, window: Optional[int],
+                             parts: Optional[int] = None) -> None:
+        n, h, width = q_cat.shape
+        if h != num_heads or cache_rows.shape[-1] != width or out.shape != (n, h, rank) or out.dtype != torch.bfloat16:
+            raise KernelError(f"latent_attention_mma: q {tuple(q_cat.shape)}, cache {tuple(cache_rows.shape)}, out {tuple(out.shape)} do not fit")
+        if parts is None:
+            parts = self.latent_attention_parts(meta.num_seqs, meta.max_q_len, h, meta.max_ctx, window)
+        part_o = part_ml = 0
+        if parts > 1:
+            scratch = self.attention_scratch(q_cat.device, n * h * parts * (rank + 2))
+            part_o = scratch.data_ptr()
+            part_ml = part_o + n * h * parts * rank * 4
+        bt = meta.block_table
+        fn = _fn("latent_attention_mma", "iian_latent_attention_mma",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+        _check(fn(_cuda(q_cat, "q_cat"), _cuda(cache_rows, "latent cache"), _cuda(out, "attention out"), part_o, part_ml,
+                  _cuda(sink, "sink", torch.float32), _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _cuda(meta.seq_of_token, "seq_of_token", torch.int32), _cuda(bt, "block table", torch.int32), bt.shape[1],
+                  n, meta.num_seqs, meta.max_q_len, h, rank, width, cache_rows.shape[1], cache_rows.shape[0], scale, window or 0,
+                  parts, _stream()), "latent_attention_mma")
+        if parts > 1:
+            LAUNCHES[0] += 1
+
     # ---- routed experts (csrc/moe.cu) -----------------------------------------------------------------------------
     _moe_tile_rows = None
 

@@ -98,7 +98,14 @@ class LatentAttention(Mixer):
         return RowNeed(self.width, int(self.window) if self.window is not None else None)
 
     def kernel_libraries(self):
-        return ("latent_attention", "gemm_simt")
+        return ("latent_attention", "gemm_simt") + (("latent_attention_mma",) if self.dtype == torch.bfloat16 else ())
+
+    def graph_plan(self, num_seqs: int, max_ctx: int):
+        """The number of key parts of the tensor-core kernel is part of a captured graph (its grid)."""
+        k = ops.kernels()
+        if not hasattr(k, "latent_attention_parts"):
+            return None
+        return {"parts": k.latent_attention_parts(num_seqs, 1, self.nh, max_ctx, self.window)}
 
     def forward(self, x, ctx, cache, writes_cache: bool, with_extra: bool = False):
         """``x`` [N, hidden] in the activation dtype.  Returns the mixer's output [N, hidden], or with ``with_extra`` the
@@ -120,8 +127,13 @@ class LatentAttention(Mixer):
         k.head_linear(qd, 0, self.dim + self.rot, self.w_uk, self.dim * self.rank, self.rank, 1,
                       q_cat.view(n, self.nh * self.width), 0, self.width, num_heads=self.nh, n_in=self.dim, n_out=self.rank)
         lat = ctx.buf("latent_ctx", (n, self.nh, self.rank), self.dtype)
-        k.latent_attention(q_cat, cache.rows, lat, self.sink, meta, num_heads=self.nh, rank=self.rank, scale=self.scale,
-                           window=self.window)
+        if hasattr(k, "latent_attention_mma_ok") and k.latent_attention_mma_ok(q_cat, cache.rows, self.rank):
+            plan = ctx.graph_plan(self)
+            k.latent_attention_mma(q_cat, cache.rows, lat, self.sink, meta, num_heads=self.nh, rank=self.rank, scale=self.scale,
+                                   window=self.window, parts=plan["parts"] if plan else None)
+        else:
+            k.latent_attention(q_cat, cache.rows, lat, self.sink, meta, num_heads=self.nh, rank=self.rank, scale=self.scale,
+                               window=self.window)
         # o_g = Wuv_g (sum_j p_j c_j)
         heads = ctx.buf("latent_heads", (n, self.nh * self.vdim), self.dtype)
         k.head_linear(lat.view(n, self.nh * self.rank), 0, self.rank, self.w_uv, self.vdim * self.rank, 1, self.rank,

@@ -108,8 +108,13 @@ def paged_meta(ctx_lens, q_lens, page_size, n_pages, seed=0):
             bt[s, b] = order.pop()
         positions += list(range(c - ql, c))
         seq += [s] * ql
+    cu = [0]
+    for ql in q_lens:
+        cu.append(cu[-1] + ql)
     return SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
                            seq_of_token=torch.tensor(seq, dtype=torch.int32, device=DEV),
+                           cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), num_seqs=len(ctx_lens), max_q_len=max(q_lens),
+                           max_ctx=max(ctx_lens),
                            block_table=bt.to(DEV), ctx_len=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)), bt
 
 
@@ -122,28 +127,39 @@ def plain_latent_rows(q, rows, sink, scale, window, rank, pos):
     return torch.einsum("hj,jr->hr", p[:, 0], rows[:, :rank])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window, far", [(40, False), (None, True), (33, False)])
-def test_latent_attention_sees_the_window_exactly(dtype, window, far):
+def attend(kernel, q, cache, out, sink, meta, **kw):
+    """The general kernel, or the tensor-core one with its keys in one part or cut into three."""
+    if kernel == "general":
+        K().latent_attention(q, cache, out, sink, meta, **kw)
+    else:
+        assert K().latent_attention_mma_ok(q, cache, kw["rank"])
+        K().latent_attention_mma(q, cache, out, sink, meta, parts=1 if kernel == "mma" else 3, **kw)
+
+
+@pytest.mark.parametrize("dtype, kernel, rank, rot", [("float32", "general", 24, 8), ("bfloat16", "general", 24, 8),
+                                                      ("bfloat16", "mma", 64, 16), ("bfloat16", "mma3", 64, 16),
+                                                      ("bfloat16", "mma", 128, 32), ("bfloat16", "mma3", 512, 64)])
+@pytest.mark.parametrize("window, far", [(40, False), (None, True), (33, False), (64, False)])
+def test_latent_attention_sees_the_window_exactly(dtype, kernel, rank, rot, window, far):
     """One key is made to stand out (its row is aligned with the query, scaled up): just inside the window it must
     carry the output, one step further out it must vanish; without a window a key hundreds of positions back counts.
     Queries sit at page borders and in the middle; once as the last rows of a prompt's portion, once as single
     decoded tokens."""
-    heads, rank, rot, page = 3, 24, 8, 16
+    heads, page = (3 if rank < 512 else 5), 16
     width = rank + rot
     g = torch.Generator().manual_seed(5)
     ctx = [300, 97, 64, 65]
-    for q_lens in ([20, 5, 64, 2], [1, 1, 1, 1]):
+    for q_lens in ([20, 5, 64, 2], [1, 1, 1, 1], [1, 30, 1, 1]):
         meta, bt = paged_meta(ctx, q_lens, page, 40, seed=len(q_lens))
-        seqs = [torch.randn(c, width, generator=g) * 0.3 for c in ctx]
+        seqs = [torch.randn(c, width, generator=g) * 0.3 for c in ctx]                   # rows of the cache, per sequence
         qs = []
         for s, (c, ql) in enumerate(zip(ctx, q_lens)):
-            q = torch.randn(ql, heads, width, generator=g) * 0.3
+            q = torch.randn(ql, heads, width, generator=g) * 0.3 * (32.0 / width) ** 0.5
             p_last = c - 1
             for off, head in (((window - 1) if window else (p_last - 3 if far else 7), 0), ((window if window else 11), 1)):
                 j = p_last - off
                 if j >= 0:
-                    direction = torch.randn(width, generator=g)
+                    direction = torch.randn(width, generator=g) * (32.0 / width) ** 0.5
                     seqs[s][j] = direction * 1.5
                     q[-1, head] = direction * 4.0            # the last query's head looks straight at key j
             qs.append(q)
@@ -152,10 +168,9 @@ def test_latent_attention_sees_the_window_exactly(dtype, window, far):
         for s, rows in enumerate(seqs):
             for j in range(rows.shape[0]):
                 cache[bt[s, j // page], j % page] = rows[j].to(DT[dtype])
-        sink = torch.tensor([0.5, -1.0, 2.0])
         out = torch.empty(q_all.shape[0], heads, rank, device=DEV, dtype=DT[dtype])
-        K().latent_attention(q_all.to(DEV), cache.to(DEV), out, sink.to(DEV), meta, num_heads=heads, rank=rank, scale=0.2,
-                             window=window)
+        sink = torch.tensor([0.5, -1.0, 2.0, 0.0, 1.0][:heads])
+        attend(kernel, q_all.to(DEV), cache.to(DEV), out, sink.to(DEV), meta, num_heads=heads, rank=rank, scale=0.2, window=window)
         t0 = 0
         for s, (c, ql) in enumerate(zip(ctx, q_lens)):
             rows = seqs[s].to(DT[dtype]).double()
@@ -165,7 +180,7 @@ def test_latent_attention_sees_the_window_exactly(dtype, window, far):
                 close(out[t0 + i], want, dtype, f"sequence {s} position {pos} (window {window}, q_lens {q_lens})")
             t0 += ql
         # without the sink the weights sum to one
-        K().latent_attention(q_all.to(DEV), cache.to(DEV), out, None, meta, num_heads=heads, rank=rank, scale=0.2, window=window)
+        attend(kernel, q_all.to(DEV), cache.to(DEV), out, None, meta, num_heads=heads, rank=rank, scale=0.2, window=window)
         rows = seqs[0].to(DT[dtype]).double()
         sc = (q_all[q_lens[0] - 1].double() @ rows.T) * 0.2
         vis = plain.window_mask(ctx[0], window)[ctx[0] - 1]
