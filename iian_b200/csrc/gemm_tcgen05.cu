@@ -48,6 +48,13 @@ struct TcExtra {
     float * res;
     const float * norm_w;
     float * out_partial;
+    // Grouped form (single-SM kernel only; null: one weight matrix for all rows).  The rows of x are sorted by group;
+    // g_tiles holds the number of row tiles and then (group, first row) per row tile of 128 rows, g_offsets [groups + 1]
+    // the first row of every group; group e multiplies with rows [e * g_rows, (e + 1) * g_rows) of w.  A row tile
+    // reads 128 rows from its first row on and stores only those that belong to its group.
+    const int * g_tiles;
+    const int * g_offsets;
+    int g_rows;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -239,7 +246,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const int m_tiles = (T + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const bool grouped = ex.g_tiles != nullptr;
+    const int m_tiles = grouped ? ex.g_tiles[0] : (T + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
     const int num_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
@@ -261,7 +269,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
         // ---- producer: the stage ring runs on across tiles -------------------------------------------
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            const int mt = tile % m_tiles;
+            const int m0 = grouped ? ex.g_tiles[2 + 2 * mt] : mt * TC_BM;
+            const int n0 = (tile / m_tiles) * BN + (grouped ? ex.g_tiles[1 + 2 * mt] * ex.g_rows : 0);     // row of w
             for (int kb = 0; kb < num_kb; kb++, it++) {
                 const int s = it % STAGES;
                 const unsigned phase = (it / STAGES) & 1;
@@ -303,7 +313,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, use++) {
             const int buf = use & 1;
             const unsigned acc_phase = (use >> 1) & 1;
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            const int mt = tile % m_tiles;
+            const int m0 = grouped ? ex.g_tiles[2 + 2 * mt] : mt * TC_BM, n0 = (tile / m_tiles) * BN;
+            const int row_end = grouped ? min(T, ex.g_offsets[ex.g_tiles[1 + 2 * mt] + 1]) : T;
             if (!mbar_wait(smem_addr(&acc_full[buf]), acc_phase)) {
                 if (lane == 0) { status->code = 3; status->where = use; }
                 failed = 1;
@@ -312,7 +324,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             float rs = 1.0f;
-            if (ex.in_partial != nullptr && row < T) {          // this row's factor: its partial sums in a fixed order
+            if (ex.in_partial != nullptr && row < row_end) {          // this row's factor: its partial sums in a fixed order
                 float a = 0.0f;
                 for (int i = 0; i < ex.in_tiles; i++) a += ex.in_partial[(size_t) row * ex.in_tiles + i];
                 rs = rsqrtf(a * ex.inv_width + ex.eps);
@@ -323,7 +335,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
                 unsigned r[32];
                 tc_ld32(tmem_base + ((unsigned) (q * 32) << 16) + (unsigned) (buf * BN + c0), r);
                 tc_wait_ld();
-                if (row < T) {
+                if (row < row_end) {
                     if constexpr (EPI == EPI_RESNORM)
                         sq += epilogue_resnorm32(r, reinterpret_cast<__nv_bfloat16 *>(out), ex.res, ex.norm_w, row, n0 + c0, N, rs);
                     else
@@ -331,7 +343,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(
                 }
             }
             if constexpr (EPI == EPI_RESNORM) {
-                if (row < T) ex.out_partial[(size_t) row * n_tiles + tile / m_tiles] = sq;
+                if (row < row_end) ex.out_partial[(size_t) row * n_tiles + tile / m_tiles] = sq;
             }
             tc_fence_before();
             __syncwarp();
@@ -560,7 +572,7 @@ static int make_map(CUtensorMap * map, const void * base, int rows, int K, int b
 
 template <int BN, int STAGES, int EPI, typename OutT>
 static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out, int T, int N, int K, int ldo, TcStatus * status,
-                     const TcExtra & ex, cudaStream_t stream) {
+                     const TcExtra & ex, cudaStream_t stream, int row_tile_bound = 0) {
     constexpr size_t smem = (size_t) STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -568,7 +580,8 @@ static int launch_tc(const CUtensorMap & ma, const CUtensorMap & mb, void * out,
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
-    const int tiles = ((T + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    // the grouped form learns its number of row tiles on the device; the grid is sized by the caller's bound
+    const int tiles = (row_tile_bound > 0 ? row_tile_bound : (T + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -664,6 +677,35 @@ static int tc_entry(const void * x, const void * w, void * out, int out_dtype, i
         return launch_tc<128, 6, EPI_STORE, float>(ma, mb, out, T, N, K, ldo, st, ex, stream);
     }
     return IIAN_ERR_DTYPE;
+}
+
+// The grouped product: x [T, K] bf16 with its rows sorted by group, w [groups * N, K] bf16 (group e's matrix in rows
+// e * N ..), out [T, N] or, with epilogue 1, [T, N / 2]; tiles = {row tiles, then (group, first row) per row tile of 128
+// rows}, offsets [groups + 1], both on the device; max_tiles bounds the row tiles (it sizes the grid).  bn: 128 or 256.
+IIAN_API int iian_gemm_tcgen05_grouped(const void * x, const void * w, void * out, int out_dtype, int T, int N, int groups, int K,
+                                       int epilogue, int bn, int * status, const int * tiles, const int * offsets, int max_tiles,
+                                       cudaStream_t stream) {
+    if (T <= 0 || N <= 0 || groups <= 0 || max_tiles <= 0) return IIAN_OK;
+    if (K <= 0 || K % 8 != 0 || tiles == nullptr || offsets == nullptr || status == nullptr) return IIAN_ERR_SHAPE;
+    if (((uintptr_t) x & 15) || ((uintptr_t) w & 15)) return IIAN_ERR_ALIGN;
+    if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU8) return IIAN_ERR_SHAPE;
+    if (epilogue == EPI_SWIGLU8 && N % 16 != 0) return IIAN_ERR_SHAPE;
+    if (bn != 128 && bn != 256) return IIAN_ERR_SHAPE;
+    if (out_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    if ((long long) groups * N > 2147483647LL) return IIAN_ERR_LIMIT;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, x, T, K, TC_BM);
+    if (rc != IIAN_OK) return rc;
+    rc = make_map(&mb, w, groups * N, K, bn);
+    if (rc != IIAN_OK) return rc;
+    TcStatus * st = (TcStatus *) status;
+    const int ldo = epilogue == EPI_SWIGLU8 ? N / 2 : N;
+    const TcExtra ex = {nullptr, 0, 0.0f, 0.0f, nullptr, nullptr, nullptr, tiles, offsets, N};
+    if (bn == 256)
+        return epilogue == EPI_STORE ? launch_tc<256, 4, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream, max_tiles)
+                                     : launch_tc<256, 4, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream, max_tiles);
+    return epilogue == EPI_STORE ? launch_tc<128, 6, EPI_STORE, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream, max_tiles)
+                                 : launch_tc<128, 6, EPI_SWIGLU8, __nv_bfloat16>(ma, mb, out, T, N, K, ldo, st, ex, stream, max_tiles);
 }
 
 // x: [T, K] bf16, w: [N, K] bf16; out: [T, N] (epilogue 0) or [T, N / 2] (epilogue 1: SiLU(gate) * up over

@@ -49,9 +49,9 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, long long ld
 }
 
 // One block.  offsets: [E + 1] first sorted row of each expert; pos: [M] sorted row of each (token, choice);
-// tiles: [2 * max_tiles + 1]: n_tiles, then (expert, first row) per row tile of kTileM rows.
+// tiles: [2 * max_tiles + 1]: n_tiles, then (expert, first row) per row tile of tile_rows rows.
 __global__ void moe_plan_kernel(const int * __restrict__ ids, int M, int E, int * __restrict__ offsets, int * __restrict__ pos,
-                                int * __restrict__ tiles, int max_tiles) {
+                                int * __restrict__ tiles, int max_tiles, int tile_rows) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ int sm[];               // counts [E], cursor [E]
@@ -66,7 +66,7 @@ __global__ void moe_plan_kernel(const int * __restrict__ ids, int M, int E, int 
         for (int e = 0; e < E; e++) {
             offsets[e] = run;
             cursor[e] = run;
-            for (int r = 0; r < counts[e] && nt < max_tiles; r += kTileM) {
+            for (int r = 0; r < counts[e] && nt < max_tiles; r += tile_rows) {
                 tiles[1 + 2 * nt] = e;
                 tiles[2 + 2 * nt] = run + r;
                 nt++;
@@ -116,7 +116,8 @@ __device__ __forceinline__ float moe_act(float z, int act) {
 
 // Rows [r0, r0 + rows) of x (sorted by expert) times expert e's weight block w[e] ([n_out, K], row-major):
 // out[r, m] = sum_k x[r, k] * w[e][m, k];  with GATED, w2[e] is a second block of the same shape and
-// out[r, m] = act(x . w[e][m]) * (x . w2[e][m]).
+// out[r, m] = act(x . w[e][m]) * (x . w2[e][m]); with GATED and w2 == w, an expert's block holds both, 2 n_out rows in
+// groups of 16: 8 rows of the first, then the 8 rows of the second for the same features.
 template <typename A, typename WT, bool GATED>
 __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restrict__ x, const WT * __restrict__ w,
                                                                const WT * __restrict__ w2, A * __restrict__ out,
@@ -134,8 +135,9 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restr
     const int m0 = blockIdx.x * kTileN;
     const int tx = tid % 16, ty = tid / 16;
     const int lrow = tid / 4, lk = (tid % 4) * 4;
-    const WT * we = w + (size_t) e * n_out * K;
-    const WT * w2e = GATED ? w2 + (size_t) e * n_out * K : nullptr;
+    const bool il = GATED && w2 == w;
+    const WT * we = w + (size_t) e * n_out * K * (il ? 2 : 1);
+    const WT * w2e = GATED ? (il ? we + (size_t) 8 * K : w2 + (size_t) e * n_out * K) : nullptr;
     float acc[4][4], acc2[GATED ? 4 : 1][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
@@ -150,8 +152,9 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restr
             const int k = k0 + lk + q;
             const int r = r0 + lrow, m = m0 + lrow;
             xs[lk + q][lrow] = (r < r_end && k < K) ? to_f32(x[(size_t) r * K + k]) : 0.0f;
-            ws[lk + q][lrow] = (m < n_out && k < K) ? to_f32(we[(size_t) m * K + k]) : 0.0f;
-            if (GATED) w2s[lk + q][lrow] = (m < n_out && k < K) ? to_f32(w2e[(size_t) m * K + k]) : 0.0f;
+            const size_t wr = il ? (size_t) (m / 8) * 16 + m % 8 : (size_t) m;       // row of the weight block
+            ws[lk + q][lrow] = (m < n_out && k < K) ? to_f32(we[wr * K + k]) : 0.0f;
+            if (GATED) w2s[lk + q][lrow] = (m < n_out && k < K) ? to_f32(w2e[wr * K + k]) : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -205,10 +208,12 @@ IIAN_API int iian_moe_route(const float * logits, long long ld, int E, int top, 
 }
 
 // ids [M] -> offsets [E + 1], pos [M], tiles [1 + 2 * max_tiles]
-IIAN_API int iian_moe_plan(const int * ids, int M, int E, int * offsets, int * pos, int * tiles, int max_tiles, cudaStream_t stream) {
+IIAN_API int iian_moe_plan(const int * ids, int M, int E, int * offsets, int * pos, int * tiles, int max_tiles, int tile_rows,
+                           cudaStream_t stream) {
     if (M <= 0) return IIAN_OK;
-    if (E <= 0 || E > 2048 || max_tiles < (M + kTileM - 1) / kTileM + E) return IIAN_ERR_SHAPE;
-    return iian_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t) 2 * E * sizeof(int), stream, ids, M, E, offsets, pos, tiles, max_tiles);
+    if (E <= 0 || E > 2048 || tile_rows <= 0 || max_tiles < (M + tile_rows - 1) / tile_rows + E) return IIAN_ERR_SHAPE;
+    return iian_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t) 2 * E * sizeof(int), stream, ids, M, E, offsets, pos, tiles,
+                       max_tiles, tile_rows);
 }
 
 IIAN_API int iian_moe_scatter(const void * h, const int * pos, const float * wts, void * xs, int act_dtype, int N, int W, int top,
@@ -229,7 +234,9 @@ IIAN_API int iian_moe_combine(const void * ys, const int * pos, void * out, int 
     return IIAN_ERR_DTYPE;
 }
 
-// x [M, K] sorted by expert; w (and w2, for the gated form) [E, n_out, K]; out [M, n_out]; act: 0 silu, 1 gelu (tanh)
+// x [M, K] sorted by expert; w (and w2, for the gated form) [E, n_out, K]; out [M, n_out]; act: 0 silu, 1 gelu (tanh).
+// w2 == w: the gated form over blocks [E, 2 n_out, K] that hold both matrices interleaved in groups of 8 rows.
+// The plan's row tiles must be of iian_moe_tile_rows() rows.
 IIAN_API int iian_moe_grouped_gemm(const void * x, const void * w, const void * w2, void * out, const int * offsets, const int * tiles,
                                    int max_tiles, int act_dtype, int w_dtype, int n_out, int K, int act, cudaStream_t stream) {
     if (max_tiles <= 0 || n_out <= 0) return IIAN_OK;

@@ -1030,9 +1030,39 @@ class CudaKernels:
             CudaKernels._moe_tile_rows = int(lib.iian_moe_tile_rows())
         return CudaKernels._moe_tile_rows
 
-    def moe_max_tiles(self, n_rows: int, num_experts: int) -> int:
+    def moe_max_tiles(self, n_rows: int, num_experts: int, tile_rows: Optional[int] = None) -> int:
         """Upper bound of the row tiles of a grouped product over ``n_rows`` rows sorted by expert."""
-        return -(-n_rows // self.moe_tile_rows()) + num_experts
+        return -(-n_rows // (tile_rows or self.moe_tile_rows())) + num_experts
+
+    # grouped products on tcgen05 (csrc/gemm_tcgen05.cu, row tiles of 128); IIAN_MOE_TCGEN05=0: the general kernel
+    MOE_TCGEN05 = os.environ.get("IIAN_MOE_TCGEN05", "1") not in ("0", "false", "off")
+    MOE_TC_TILE_ROWS = 128
+
+    def moe_tcgen05_ok(self, dtype: torch.dtype, hidden: int, inter: int, activation: str) -> bool:
+        """Whether both grouped products of an expert feed-forward can run on the tcgen05 kernel: bfloat16, rows of 16
+        bytes' multiples for TMA, gate and up interleaved in groups of 8 with the SiLU epilogue."""
+        return (self.MOE_TCGEN05 and not self.LIBRARY_GEMM_ONLY and dtype == torch.bfloat16 and activation == "silu"
+                and hidden % 8 == 0 and inter % 8 == 0)
+
+    def moe_grouped_gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, tiles: torch.Tensor,
+                            gated: bool) -> None:
+        """Rows of ``x`` sorted by expert times that expert's block of ``w`` [E, n, K] on tcgen05; ``gated``: the block's
+        rows are gate and up interleaved in groups of 8 and ``out`` [M, n / 2] = silu(gate) * up.  The plan's row tiles
+        are of 128 rows."""
+        m, k = x.shape
+        e, n = w.shape[0], w.shape[1]
+        if w.shape[2] != k or out.shape != (m, n // 2 if gated else n) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 \
+                or out.dtype != torch.bfloat16:
+            raise KernelError(f"moe_grouped_gemm_tc: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        bn = 256 if n % 256 == 0 or n > 2048 else 128
+        status = self.tcgen05_status_buffer(x.device).data_ptr()
+        CudaKernels._tc_used = True
+        fn = _fn("gemm_tcgen05", "iian_gemm_tcgen05_grouped",
+                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                  c_void_p])
+        _check(fn(_cuda(x, "moe rows"), _cuda(w, "expert weights"), _cuda(out, "moe out"), BF16, m, n, e, k, 1 if gated else 0, bn,
+                  status, _cuda(tiles, "tiles", torch.int32), _cuda(offsets, "offsets", torch.int32), (tiles.numel() - 1) // 2,
+                  _stream()), "gemm_tcgen05_grouped")
 
     def moe_route(self, logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
         """Router logits (float32, may be a column slice) -> the ``top`` experts of each token by sigmoid score, and the scores."""
@@ -1044,14 +1074,16 @@ class CudaKernels:
         _check(fn(lp, ld, e, top, _cuda(ids, "expert ids", torch.int32), _cuda(weights, "expert weights", torch.float32), n,
                   _stream()), "moe_route")
 
-    def moe_plan(self, ids: torch.Tensor, num_experts: int, offsets: torch.Tensor, pos: torch.Tensor, tiles: torch.Tensor) -> None:
+    def moe_plan(self, ids: torch.Tensor, num_experts: int, offsets: torch.Tensor, pos: torch.Tensor, tiles: torch.Tensor,
+                 tile_rows: Optional[int] = None) -> None:
         m = ids.numel()
         max_tiles = (tiles.numel() - 1) // 2
         if offsets.numel() != num_experts + 1 or pos.numel() != m:
             raise KernelError("moe_plan: offsets [E + 1], pos [M]")
-        fn = _fn("moe", "iian_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+        fn = _fn("moe", "iian_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
         _check(fn(_cuda(ids, "expert ids", torch.int32), m, num_experts, _cuda(offsets, "offsets", torch.int32),
-                  _cuda(pos, "pos", torch.int32), _cuda(tiles, "tiles", torch.int32), max_tiles, _stream()), "moe_plan")
+                  _cuda(pos, "pos", torch.int32), _cuda(tiles, "tiles", torch.int32), max_tiles,
+                  tile_rows or self.moe_tile_rows(), _stream()), "moe_plan")
 
     def moe_scatter(self, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, xs: torch.Tensor, top: int) -> None:
         n, w = h.shape
@@ -1064,9 +1096,10 @@ class CudaKernels:
     def moe_grouped_gemm(self, x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], out: torch.Tensor,
                          offsets: torch.Tensor, tiles: torch.Tensor, activation: str = "silu") -> None:
         """Rows of ``x`` sorted by expert times that expert's block of ``w`` [E, n_out, K]; with ``w2`` the gated form
-        ``act(x . w) * (x . w2)``."""
+        ``act(x . w) * (x . w2)``; with ``w2 is w`` the blocks are [E, 2 n_out, K] and hold both matrices interleaved in
+        groups of 8 rows."""
         m, k = x.shape
-        n_out = w.shape[1]
+        n_out = w.shape[1] // 2 if w2 is w else w.shape[1]
         if w.shape[2] != k or out.shape != (m, n_out) or (w2 is not None and w2.shape != w.shape) or out.dtype != x.dtype:
             raise KernelError(f"moe_grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
         fn = _fn("moe", "iian_moe_grouped_gemm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

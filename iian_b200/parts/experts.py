@@ -43,7 +43,7 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: sigmoid scores that weigh the expert's input are what is built")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"routed_experts: top {self.top} of {self.experts} experts")
-        self.w_router = self.w_gate = self.w_up = self.w_down = None
+        self.w_router = self.w_gate = self.w_up = self.w_down = self.w_gate_up = None
         self.extra_rows = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -57,8 +57,16 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self._router = tensors["router"]
         self.w_router = self._router.contiguous()
-        for name in ("gate", "up", "down"):
-            setattr(self, f"w_{name}", torch.stack([tensors[f"e{e}.{name}"] for e in range(self.experts)]).contiguous())
+        gate = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)])
+        up = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)])
+        self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        if self.inter % 8 == 0:
+            # gate and up rows interleaved in groups of 8, the layout a product kernel wants for act(gate) * up in its epilogue
+            E, F, W = self.experts, self.inter, self.hidden
+            self.w_gate_up = torch.stack([gate.view(E, F // 8, 8, W), up.view(E, F // 8, 8, W)], dim=2).reshape(E, 2 * F, W).contiguous()
+            self.w_gate = self.w_up = None
+        else:
+            self.w_gate_up, self.w_gate, self.w_up = None, gate.contiguous(), up.contiguous()
 
     def stack_rows(self, rows: torch.Tensor) -> None:
         self.extra_rows = rows
@@ -68,7 +76,7 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(ws, dim=0).contiguous()
 
     def kernel_libraries(self):
-        return ("moe", "gemm_simt")
+        return ("moe", "gemm_simt")        # in bfloat16 the products' fast forms come with gemm_simt (the grouped tcgen05 one too)
 
     def forward(self, x, ctx, with_extra: bool = False):
         k = ops.kernels()
@@ -83,17 +91,27 @@ class RoutedExperts(FeedForward):
         ids = ctx.buf("expert_ids", (n, top), torch.int32)
         wts = ctx.buf("expert_weights", (n, top), torch.float32)
         k.moe_route(logits[:, :E], top, ids, wts)
-        max_tiles = k.moe_max_tiles(m, E)
+        on_tc = (self.w_gate_up is not None and hasattr(k, "moe_tcgen05_ok")
+                 and k.moe_tcgen05_ok(self.dtype, self.hidden, self.inter, self.activation))
+        tile_rows = k.MOE_TC_TILE_ROWS if on_tc else k.moe_tile_rows()
+        max_tiles = k.moe_max_tiles(m, E, tile_rows)
         offsets = ctx.buf("expert_offsets", (E + 1,), torch.int32)
         pos = ctx.buf("expert_pos", (m,), torch.int32)
         tiles = ctx.buf("expert_tiles", (1 + 2 * max_tiles,), torch.int32)
-        k.moe_plan(ids, E, offsets, pos, tiles)
+        k.moe_plan(ids, E, offsets, pos, tiles, tile_rows)
         xs = ctx.buf("expert_in", (m, self.hidden), self.dtype)
         k.moe_scatter(x, pos, wts, xs, top)
         act = ctx.buf("expert_act", (m, self.inter), self.dtype)
-        k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation)
         ys = ctx.buf("expert_out", (m, self.hidden), self.dtype)
-        k.moe_grouped_gemm(act, self.w_down, None, ys, offsets, tiles)
+        if on_tc:
+            k.moe_grouped_gemm_tc(xs, self.w_gate_up, act, offsets, tiles, gated=True)
+            k.moe_grouped_gemm_tc(act, self.w_down, ys, offsets, tiles, gated=False)
+        else:
+            if self.w_gate_up is not None:
+                k.moe_grouped_gemm(xs, self.w_gate_up, self.w_gate_up, act, offsets, tiles, self.activation)
+            else:
+                k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation)
+            k.moe_grouped_gemm(act, self.w_down, None, ys, offsets, tiles)
         out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
         k.moe_combine(ys, pos, out, top)
         if with_extra:

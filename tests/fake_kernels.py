@@ -220,8 +220,8 @@ class FakeKernels:
     def moe_tile_rows(self):
         return 64
 
-    def moe_max_tiles(self, n_rows, num_experts):
-        return -(-n_rows // 64) + num_experts
+    def moe_max_tiles(self, n_rows, num_experts, tile_rows=None):
+        return -(-n_rows // (tile_rows or 64)) + num_experts
 
     def moe_route(self, logits, top, ids, weights):
         s = torch.sigmoid(logits)
@@ -229,7 +229,7 @@ class FakeKernels:
         ids.copy_(order.int())
         weights.copy_(torch.gather(s, 1, order))
 
-    def moe_plan(self, ids, num_experts, offsets, pos, tiles):
+    def moe_plan(self, ids, num_experts, offsets, pos, tiles, tile_rows=None):
         flat = ids.reshape(-1).long()
         order = torch.sort(flat, stable=True).indices
         pos[order] = torch.arange(flat.numel(), dtype=pos.dtype)
@@ -243,6 +243,9 @@ class FakeKernels:
             xs[int(pos[i])] = (w[i] * h[i // top].float()).to(xs.dtype)
 
     def moe_grouped_gemm(self, x, w, w2, out, offsets, tiles, activation="silu"):
+        if w2 is w:         # gate and up interleaved in groups of 8 rows
+            v = w.view(w.shape[0], w.shape[1] // 16, 2, 8, w.shape[2])
+            w, w2 = v[:, :, 0].reshape(w.shape[0], -1, w.shape[2]), v[:, :, 1].reshape(w.shape[0], -1, w.shape[2])
         for e in range(w.shape[0]):
             a, b = int(offsets[e]), int(offsets[e + 1])
             if b <= a:

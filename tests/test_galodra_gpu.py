@@ -234,12 +234,14 @@ def test_latent_prep_and_head_products(dtype):
 
 # ---- routed experts -----------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("experts, top, n", [(5, 2, 37), (8, 1, 200), (3, 3, 1), (70, 4, 90)])
-def test_routed_experts_part(dtype, experts, top, n):
+@pytest.mark.parametrize("experts, top, n, ff", [(5, 2, 37, 48), (8, 1, 200, 48), (3, 3, 1, 50), (70, 4, 90, 48), (6, 2, 700, 128)])
+def test_routed_experts_part(dtype, experts, top, n, ff):
+    """Scores, choices, the plan, both grouped products (in bfloat16 on tcgen05 when the expert's width is a multiple of
+    8, else and in 32-bit the general kernel; several row tiles per expert in the last case) and the sum."""
     from iian_b200.config.spec import PartSpec
     from iian_b200.engine.runner import StepContext, Workspace
     from iian_b200.parts.experts import RoutedExperts
-    width, ff = 64, 48
+    width = 64
     g = torch.Generator().manual_seed(experts)
     part = RoutedExperts(PartSpec("routed_experts", {"hidden_size": width, "num_experts": experts, "top": top,
                                                      "intermediate_size": ff}), DT[dtype], torch.device(DEV))
@@ -252,9 +254,14 @@ def test_routed_experts_part(dtype, experts, top, n):
     part.bind({k: v.to(DEV) for k, v in w.items()})
     h = torch.randn(n, width, generator=g).to(DT[dtype])
     ctx = StepContext(Workspace(torch.device(DEV)))
+    from iian_b200.ops import cuda_backend
+    before = dict(cuda_backend.LAUNCHES_BY_ENTRY)
     out = part.forward(h.to(DEV), ctx)
+    served = {k for k, v in cuda_backend.LAUNCHES_BY_ENTRY.items() if v > before.get(k, 0)}
+    assert ("gemm_tcgen05_grouped" if dtype == "bfloat16" and ff % 8 == 0 else "moe_grouped_gemm") in served, served
     want = plain.routed_ff(h.double(), {k: v.double() for k, v in w.items()}, "", experts, top)
     close(out, want, dtype, f"{top} of {experts} experts, {n} tokens", rel16=3e-2, abs32=1e-5)
+    K().check_device_status()
     ids = ctx.buf("expert_ids", (n, top), torch.int32).cpu()
     want_ids = torch.topk(torch.sigmoid(h.double() @ w["router"].double().T), top, dim=-1).indices
     assert torch.equal(ids.long(), want_ids)
