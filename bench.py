@@ -136,6 +136,30 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+def design_arm(args, K: int, W: int) -> int:
+    """``--design galodra``: the design's shapes beside the Qwen3 shapes of equal size (``iian_b200/cli/workloads.py``:
+    ``GALODRA_SHAPES``, ``EQUAL_QWEN3``), decode at batch 1 / 8 / 64 from 1,024-token prompts and prefill of 2,048 tokens,
+    device-timed like the default workload; with ``--kernels`` the design's kernels alone beside their like kernels."""
+    import torch
+    from iian_b200.cli import workloads as wl
+    peaks, peak_kind = wl.load_peaks(ROOT)
+    torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    line = {"design": args.design, "dtype": "bf16", "steps": K, "warmup": W, "peaks": dict(peaks, kind=peak_kind),
+            "data": "synthetic: random weights N(0, 0.02), uniform random token ids (seed 1234)"}
+    if args.kernels:
+        from iian_b200.cli import design_kernels
+        line["kernels"] = design_kernels.run(peaks)
+    else:
+        line["shapes"] = wl.design_comparison([n for n in args.design_shapes.split(",") if n], (1, 8, 64), (PREFILL_TOKENS,),
+                                              PROMPT_LEN, K, W, peaks, cuda_graphs=not args.no_cuda_graphs)
+    sampler.stop()
+    line["clocks"] = sampler.summary()
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -149,6 +173,11 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="the headline and the end-to-end figure only")
     ap.add_argument("--skip-32b", action="store_true", help="leave out the Qwen3-32B shape")
     ap.add_argument("--skip-serve", action="store_true", help="leave out the continuous-batching workload (Qwen3-0.6B shape)")
+    ap.add_argument("--design", default="", choices=["", "galodra"],
+                    help="instead of the default workload: decode and prefill throughput of this design at layer sizes of real "
+                         "models beside the Qwen3 shape of equal size (one JSON line of its own)")
+    ap.add_argument("--design-shapes", default="g2k-dense,g2k-moe,g4k-dense")
+    ap.add_argument("--kernels", action="store_true", help="with --design: the design's kernels alone beside the like kernels of Qwen3")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -157,6 +186,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     K, W = args.steps, max(3, args.warmup)
+    if args.design:
+        return design_arm(args, K, W)
 
     import gc
     import torch

@@ -1,0 +1,236 @@
+"""The kernels of the Galodra design alone, each beside the like kernel of the Qwen3 path at equal size.
+
+    python -m iian_b200.cli.design_kernels            (or ``bench.py --design galodra --kernels``)
+
+A kernel is timed as a replayed CUDA graph of a few launches on different copies of its operands (which together exceed
+the L2), after one eager run, with a 256 MB buffer written before every replay; the median of several replays counts.
+Achieved bytes or flops are the
+algorithmic ones (what the operation has to read and write, or multiply) over that time, set against the measured copy
+bandwidth and bfloat16 product peak.
+
+Pairs (width 2048, 16 heads; latent rank 512 + 64 rotated; Qwen3 side: 16 heads of 128 on 8 KV heads):
+  decode attention   8 sequences of 4,096 cached tokens, one new token each       bytes of cache read
+  prefill attention  one sequence of 2,048 tokens                                 flops of scores and values
+  expert products    2,048 tokens x 6 of 64 experts (1,408 wide)  vs  the dense gate/up and down products of 8,448
+  sum + norm         2,048 rows: gated sum with LayerNorm  vs  residual add with RMSNorm
+  per-head products  the query into latent space and the values out of it (no like kernel on the Qwen3 path)
+"""
+from __future__ import annotations
+
+import json
+import statistics
+import sys
+from types import SimpleNamespace
+
+
+def _timed(fns, iters: int = 7) -> float:
+    """Median milliseconds of one call: the calls of ``fns`` (the same kernel on different copies of its operands, which
+    together exceed the L2) run once eagerly, are then captured into one CUDA graph, and the graph is replayed ``iters``
+    times, each time after a 256 MB buffer was written; a replay's device time over the number of calls counts.  Timing
+    a graph keeps the host's launch cost out of kernels of a few microseconds."""
+    import torch
+    if callable(fns):
+        fns = [fns]
+    flush = _timed.flush
+    if flush is None:
+        flush = _timed.flush = torch.empty(64 << 20, dtype=torch.float32, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) / len(fns))
+    return statistics.median(times)
+
+
+_timed.flush = None
+
+
+def _meta(ctx_lens, q_lens, page: int, dev):
+    import torch
+    n_blocks = [-(-c // page) for c in ctx_lens]
+    bt = torch.full((len(ctx_lens), max(n_blocks)), -1, dtype=torch.int32)
+    nxt, positions, seq, cu = 0, [], [], [0]
+    for s, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
+        bt[s, : n_blocks[s]] = torch.arange(nxt, nxt + n_blocks[s], dtype=torch.int32)
+        nxt += n_blocks[s]
+        positions += list(range(c - ql, c))
+        seq += [s] * ql
+        cu.append(cu[-1] + ql)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    return SimpleNamespace(positions=t(positions), seq_of_token=t(seq), cu_q=t(cu), ctx_len=t(ctx_lens), block_table=bt.to(dev),
+                           slots=None, num_seqs=len(ctx_lens), num_tokens=len(positions), max_q_len=max(q_lens), max_ctx=max(ctx_lens),
+                           decode_only=max(q_lens) == 1, h_q_len=list(q_lens), h_ctx_len=list(ctx_lens)), nxt
+
+
+def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
+    import torch
+    from .. import ops
+    from ..config.spec import PartSpec
+    from ..engine.runner import StepContext, Workspace
+    from ..parts.experts import RoutedExperts
+    k = ops.kernels()
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    rank, rot, dim, vdim, page, window = 512, 64, 128, 128, 16, 4096
+    lw = rank + rot
+    out = {}
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+
+    def mem_row(name, ms, nbytes):
+        out[name] = {"ms": ms, "gb_s": nbytes / ms / 1e6, "of_hbm_peak": nbytes / ms / 1e6 / hbm}
+
+    def flop_row(name, ms, flops):
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "of_bf16_peak": flops / ms / 1e9 / tfl}
+
+    # ---- decode attention --------------------------------------------------------------------------------------------
+    B, ctx = 8, 4096
+    meta, pages = _meta([ctx] * B, [1] * B, page, dev)
+    rows = torch.randn(pages, page, lw, device=dev).to(bf) * 0.3
+    q = torch.randn(B, heads, lw, device=dev).to(bf) * 0.1
+    o = torch.empty(B, heads, rank, device=dev, dtype=bf)
+    sink = torch.zeros(heads, device=dev)
+    copies = [rows.clone() for _ in range(5)]
+    ms = _timed([(lambda r=r: k.latent_attention_mma(q, r, o, sink, meta, num_heads=heads, rank=rank, scale=0.07, window=window))
+                 for r in copies])
+    mem_row("decode_attention_latent", ms, B * ctx * lw * 2)
+    del copies
+    nkv, hd = 8, 128
+    kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    q2 = torch.randn(B, heads, hd, device=dev).to(bf) * 0.1
+    o2 = torch.empty(B, heads * hd, device=dev, dtype=bf)
+    copies = [(kc.clone(), vc.clone()) for _ in range(3)]
+    ms = _timed([(lambda c=c: k.paged_attention(q2, c[0], c[1], o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                window=window)) for c in copies])
+    mem_row("decode_attention_qwen3", ms, B * ctx * 2 * nkv * hd * 2)
+    del copies
+
+    # ---- prefill attention -------------------------------------------------------------------------------------------
+    T = 2048
+    meta, pages = _meta([T], [T], page, dev)
+    rows = torch.randn(pages, page, lw, device=dev).to(bf) * 0.3
+    q = torch.randn(T, heads, lw, device=dev).to(bf) * 0.1
+    o = torch.empty(T, heads, rank, device=dev, dtype=bf)
+    pairs = T * (T + 1) / 2
+    ms = _timed(lambda: k.latent_attention_mma(q, rows, o, sink, meta, num_heads=heads, rank=rank, scale=0.07, window=window))
+    flop_row("prefill_attention_latent", ms, 2.0 * heads * (lw + rank) * pairs)
+    kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    q2 = torch.randn(T, heads, hd, device=dev).to(bf) * 0.1
+    o2 = torch.empty(T, heads * hd, device=dev, dtype=bf)
+    ms = _timed(lambda: k.paged_attention(q2, kc, vc, o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=window))
+    flop_row("prefill_attention_qwen3", ms, 4.0 * heads * hd * pairs)
+
+    # ---- expert products beside the dense products of the same active size -------------------------------------------
+    E, top, ff = 64, 6, 1408
+    part = RoutedExperts(PartSpec("routed_experts", {"hidden_size": width, "num_experts": E, "top": top, "intermediate_size": ff}),
+                         bf, dev)
+    tensors = {"router": torch.randn(E, width, device=dev).to(bf) * 0.05}
+    for e in range(E):
+        tensors[f"e{e}.gate"] = torch.randn(ff, width, device=dev).to(bf) * 0.02
+        tensors[f"e{e}.up"] = torch.randn(ff, width, device=dev).to(bf) * 0.02
+        tensors[f"e{e}.down"] = torch.randn(width, ff, device=dev).to(bf) * 0.02
+    part.bind(tensors)
+    del tensors
+    for n in (2048, 8):
+        h = torch.randn(n, width, device=dev).to(bf)
+        ctx_ = StepContext(Workspace(dev))
+        part.forward(h, ctx_)                   # sizes the buffers and leaves a plan
+        m = n * top
+        offsets, tiles = ctx_.buf("expert_offsets", (E + 1,), torch.int32), ctx_.buf("expert_tiles", (1 + 2 * k.moe_max_tiles(m, E, 128),), torch.int32)
+        xs, act, ys = ctx_.buf("expert_in", (m, width), bf), ctx_.buf("expert_act", (m, ff), bf), ctx_.buf("expert_out", (m, width), bf)
+        ms1 = _timed(lambda: k.moe_grouped_gemm_tc(xs, part.w_gate_up, act, offsets, tiles, gated=True))
+        ms2 = _timed(lambda: k.moe_grouped_gemm_tc(act, part.w_down, ys, offsets, tiles, gated=False))
+        ms_all = _timed(lambda: part.forward(h, ctx_))
+        if n >= 128:
+            flop_row(f"expert_gate_up_{n}", ms1, 2.0 * m * 2 * ff * width)
+            flop_row(f"expert_down_{n}", ms2, 2.0 * m * ff * width)
+            flop_row(f"expert_feed_forward_{n}", ms_all, 2.0 * m * 3 * ff * width)
+        else:
+            reached = len(set(ctx_.buf("expert_ids", (n, top), torch.int32).flatten().tolist()))
+            mem_row(f"expert_gate_up_{n}", ms1, reached * 2 * ff * width * 2)
+            mem_row(f"expert_down_{n}", ms2, reached * ff * width * 2)
+            mem_row(f"expert_feed_forward_{n}", ms_all, reached * 3 * ff * width * 2)
+        inter = top * ff
+        wgu = torch.randn(2 * inter, width, device=dev).to(bf) * 0.02
+        wd = torch.randn(width, inter, device=dev).to(bf) * 0.02
+        a2, y2 = torch.empty(n, inter, device=dev, dtype=bf), torch.empty(n, width, device=dev, dtype=bf)
+        fused = k.can_fuse_swiglu(h, wgu, 8)
+        gu = torch.empty(n, 2 * inter, device=dev, dtype=bf)
+
+        def dense_gate_up():
+            if fused:
+                k.linear_swiglu(h, wgu, a2)
+            else:
+                k.linear(h, wgu, gu)
+                k.swiglu(gu, a2, 8)
+        ms1 = _timed(dense_gate_up)
+        ms2 = _timed(lambda: k.linear(a2, wd, y2))
+        if n >= 128:
+            flop_row(f"dense_gate_up_{n}", ms1, 2.0 * n * 2 * inter * width)
+            flop_row(f"dense_down_{n}", ms2, 2.0 * n * inter * width)
+        else:
+            mem_row(f"dense_gate_up_{n}", ms1, 2 * inter * width * 2)
+            mem_row(f"dense_down_{n}", ms2, inter * width * 2)
+        del wgu, wd
+
+    # ---- sum + norm ----------------------------------------------------------------------------------------------------
+    n = 2048
+    x = torch.randn(n, width, device=dev)
+    sub = torch.randn(n, width, device=dev).to(bf)
+    gate = torch.randn(n, width, device=dev).to(bf)
+    gb, w, b = torch.zeros(width, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
+    o32, o16 = torch.empty(n, width, device=dev), torch.empty(n, width, device=dev, dtype=bf)
+    ms = _timed(lambda: k.gated_add_layer_norm(x, sub, gate, gb, w, b, 2.0, 1e-6, o32, o16))
+    mem_row("gated_sum_layer_norm", ms, n * width * (4 + 2 + 2 + 4 + 2))
+    ms = _timed(lambda: k.add_rms_norm(x, sub, w, 1e-6, o16))
+    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 2))
+    terms = [torch.randn(n, width, device=dev) for _ in range(5)]
+    coef = torch.ones(5, device=dev)
+    ms = _timed(lambda: k.depth_mix(terms, coef, None, False, o32, o16))
+    mem_row("depth_mix_5_terms", ms, n * width * (5 * 4 + 4 + 2))
+
+    # ---- per-head products ---------------------------------------------------------------------------------------------
+    for n in (2048, 8):
+        qd = torch.randn(n, heads * (dim + rot), device=dev).to(bf)
+        uk = torch.randn(heads * dim, rank, device=dev).to(bf) * 0.05
+        q_cat = torch.empty(n, heads * lw, device=dev, dtype=bf)
+        uks = [uk.clone() for _ in range(70 if n <= 8 else 1)]
+        ms = _timed([(lambda u=u: k.head_linear(qd, 0, dim + rot, u, dim * rank, rank, 1, q_cat, 0, lw, num_heads=heads, n_in=dim, n_out=rank))
+                     for u in uks])
+        (flop_row if n >= 128 else mem_row)(f"query_into_latent_{n}", ms, 2.0 * n * heads * dim * rank if n >= 128 else heads * dim * rank * 2)
+        lat = torch.randn(n, heads * rank, device=dev).to(bf)
+        uv = torch.randn(heads * vdim, rank, device=dev).to(bf) * 0.05
+        hv = torch.empty(n, heads * vdim, device=dev, dtype=bf)
+        uvs = [uv.clone() for _ in range(70 if n <= 8 else 1)]
+        ms = _timed([(lambda u=u: k.head_linear(lat, 0, rank, u, vdim * rank, 1, rank, hv, 0, vdim, num_heads=heads, n_in=rank, n_out=vdim))
+                     for u in uvs])
+        (flop_row if n >= 128 else mem_row)(f"values_out_of_latent_{n}", ms, 2.0 * n * heads * vdim * rank if n >= 128 else heads * vdim * rank * 2)
+    k.check_device_status()
+    return out
+
+
+def main(argv=None) -> int:
+    from . import workloads
+    peaks, kind = workloads.load_peaks()
+    print(json.dumps({"peaks": dict(peaks, kind=kind), "kernels": run(peaks)}, indent=1))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

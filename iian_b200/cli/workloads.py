@@ -36,6 +36,35 @@ SHAPES: Dict[str, dict] = {
                 num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
                 max_position_embeddings=40960, tie_word_embeddings=False),
 }
+
+
+def _galodra_shape(width, heads, layers, ff=0, experts=0, top=0, expert_ff=0, vocab=32768, window=4096):
+    mixer = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+             "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": window}}
+    mlp = ({"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}} if experts
+           else {"kind": "dense", "ff": ff})
+    return {"architecture": "Galodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": dict(mlp)} for _ in range(layers)]}
+
+
+def _qwen3_shape(hidden, heads, layers, inter, vocab=32768):
+    return dict(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960,
+                tie_word_embeddings=True)
+
+
+# Galodra shapes with layer sizes of real models (latent rank 512 + 64 rotated, heads of 128 + 64, window 4096), eight
+# layers each, and beside each the Qwen3 dense shape of equal width, heads, layers and (active) feed-forward size.
+GALODRA_SHAPES: Dict[str, dict] = {
+    "g2k-dense": _galodra_shape(2048, 16, 8, ff=8192),
+    "g2k-moe": _galodra_shape(2048, 16, 8, experts=64, top=6, expert_ff=1408),
+    "g4k-dense": _galodra_shape(4096, 32, 8, ff=12288),
+}
+EQUAL_QWEN3: Dict[str, dict] = {
+    "g2k-dense": _qwen3_shape(2048, 16, 8, 8192),
+    "g2k-moe": _qwen3_shape(2048, 16, 8, 6 * 1408),
+    "g4k-dense": _qwen3_shape(4096, 32, 8, 12288),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -57,10 +86,16 @@ def load_peaks(root: Optional[str] = None):
 
 def shape_config(name: str, layers: Optional[int] = None):
     from ..models.qwen3 import qwen3_config_from_dict
+    if name in GALODRA_SHAPES:
+        from ..models.galodra import galodra_config_from_dict
+        raw = dict(GALODRA_SHAPES[name])
+        if layers:
+            raw["layers"] = raw["layers"][:layers]
+        return galodra_config_from_dict(raw)
     try:
         raw = dict(SHAPES[name])
     except KeyError:
-        raise ValueError(f"unknown shape '{name}' ({' | '.join(SHAPES)})") from None
+        raise ValueError(f"unknown shape '{name}' ({' | '.join(list(SHAPES) + list(GALODRA_SHAPES))})") from None
     if layers:
         raw["num_hidden_layers"] = layers
     return qwen3_config_from_dict(raw)
@@ -71,7 +106,13 @@ def random_model(name: str, dtype: str = "bfloat16", device="cuda:0", seed: int 
     from ..config.registry import get_architecture
     from ..engine.model import Model
     cfg = shape_config(name, layers)
-    return Model.from_random(get_architecture("Qwen3ForCausalLM"), cfg, seed=seed, dtype=dtype, device=device, norm_jitter=0.0)
+    arch = "Galodra" if name in GALODRA_SHAPES else "Qwen3ForCausalLM"
+    return Model.from_random(get_architecture(arch), cfg, seed=seed, dtype=dtype, device=device, norm_jitter=0.0)
+
+
+def accounting_for(cfg, dtype_bytes: int = 2):
+    """Bytes and flops of a step for a configuration of any built-in architecture."""
+    return GalodraAccounting(cfg, dtype_bytes) if hasattr(cfg, "postln_alpha") else Accounting(cfg, dtype_bytes)
 
 
 class Accounting:
@@ -92,6 +133,49 @@ class Accounting:
         c = self.cfg
         return 2.0 * tokens * c.num_hidden_layers * self.layer_w + 2.0 * self.head_w \
             + c.num_hidden_layers * 4.0 * c.q_size * tokens * (tokens + 1) / 2
+
+
+class GalodraAccounting:
+    """Bytes and flops of a Galodra step.  A decode step reads every dense weight once, of routed experts those that the
+    batch is expected to reach (``E (1 - (1 - top / E)^batch)`` of E), and of the latent cache the rows inside each
+    layer's window."""
+
+    def __init__(self, cfg, dtype_bytes: int = 2):
+        self.cfg, self.b = cfg, dtype_bytes
+        self.head_w = cfg.vocab * cfg.width
+
+    def _layer(self, lc, batch: int):
+        """(weights read by a step of ``batch`` tokens, weights a token multiplies with) of one layer."""
+        w, m = self.cfg.width, lc.mixer
+        mix = w * (m.heads * (m.dim + m.rot_dim) + m.kv_rank + m.rot_dim + w) + m.heads * (m.dim + m.vdim) * m.kv_rank \
+            + w * m.heads * m.vdim
+        if lc.mlp is None:
+            return mix, mix
+        if lc.mlp.kind == "dense":
+            ff = 3 * w * lc.mlp.ff + w * w
+            return mix + ff, mix + ff
+        e, top = lc.mlp.experts, lc.mlp.top
+        reached = e * (1.0 - (1.0 - top / e) ** batch)
+        shared = (e + w) * w
+        return mix + shared + reached * 3 * w * lc.mlp.ff, mix + shared + top * 3 * w * lc.mlp.ff
+
+    def decode_bytes(self, batch: int, ctx_avg: float) -> float:
+        total = self.head_w * self.b
+        for lc in self.cfg.layers:
+            total += self._layer(lc, batch)[0] * self.b
+            keys = min(ctx_avg, lc.mixer.window) if lc.mixer.window else ctx_avg
+            total += batch * keys * (lc.mixer.kv_rank + lc.mixer.rot_dim) * self.b
+        return total
+
+    def prefill_flops(self, tokens: int) -> float:
+        total = 2.0 * self.head_w
+        for lc in self.cfg.layers:
+            m = lc.mixer
+            total += 2.0 * tokens * self._layer(lc, 1)[1]
+            w = m.window or tokens
+            pairs = tokens * (tokens + 1) / 2 if tokens <= w else w * (w + 1) / 2 + (tokens - w) * w
+            total += 2.0 * m.heads * (2 * m.kv_rank + m.rot_dim) * pairs
+        return total
 
 
 class TokenSource:
@@ -192,7 +276,7 @@ def decode_and_prefill_points(model, batches: Sequence[int], prompt_len: int, st
     roofline fractions: ``{"decode": {B: {...}}, "prefill": {T: {...}}}``."""
     from ..config.engine import EngineConfig, SchedulerConfig
     from ..engine.engine import Engine
-    acc = Accounting(model.config)
+    acc = accounting_for(model.config)
     max_b = max(batches) if batches else 1
     per_req = prompt_len + warmup + steps + 48
     longest = max([per_req] + list(prefill_tokens))
@@ -314,4 +398,38 @@ def serving_workload(shape: str = "0.6b", n_requests: int = 256, kv_cache_tokens
     out = run_serving(engine, reqs, check_alone)
     out.update({"shape": shape, "kv_cache_tokens": kv_cache_tokens, "max_num_seqs": max_num_seqs,
                 "max_num_batched_tokens": max_num_batched_tokens})
+    return out
+
+
+# ---- one design beside another of equal size ------------------------------------------------------------------------
+def design_comparison(names: Sequence[str], batches: Sequence[int], prefill_tokens: Sequence[int], prompt_len: int, steps: int,
+                      warmup: int, peaks: dict, device="cuda:0", cuda_graphs: bool = True) -> dict:
+    """Decode and prefill throughput of each named Galodra shape and of the Qwen3 shape of equal size, random weights:
+    ``{name: {"galodra": {...}, "qwen3": {...}}}`` with tokens/s and roofline fractions per point."""
+    import gc
+    import torch
+    from ..config.registry import get_architecture
+    from ..engine.model import Model
+    from ..models.qwen3 import qwen3_config_from_dict
+    out = {}
+    for name in names:
+        row = {}
+        for side in ("galodra", "qwen3"):
+            if side == "galodra":
+                model = random_model(name, "bfloat16", device)
+            else:
+                model = Model.from_random(get_architecture("Qwen3ForCausalLM"), qwen3_config_from_dict(EQUAL_QWEN3[name]), seed=0,
+                                          dtype="bfloat16", device=device, norm_jitter=0.0)
+            res = decode_and_prefill_points(model, batches, prompt_len, steps, warmup, prefill_tokens, prompt_len + 512, peaks,
+                                            cuda_graphs=cuda_graphs)
+            eng = res.pop("engine")
+            eng.runner.check_device_status()
+            row[side] = {"weight_gb": model.weight_bytes / 1e9,
+                         "decode": {str(b): {k: r[k] for k in ("tokens_per_s", "ms_per_step", "roofline_frac", "launches")}
+                                    for b, r in res["decode"].items()},
+                         "prefill": {str(t): {k: r[k] for k in ("tokens_per_s", "ms", "tflops", "frac")} for t, r in res["prefill"].items()}}
+            del eng, res, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[name] = row
     return out

@@ -107,6 +107,97 @@ __global__ void head_linear_kernel(const A * __restrict__ in, long long ld_in, i
     }
 }
 
+// The same products for steps of up to 8 tokens in bfloat16, where the weights should cross the memory system once and
+// as many of their bytes as possible should be in flight at once: every load is 16 bytes, a block takes one head and a
+// slab of its outputs for ALL tokens, and the inputs of the tokens wait in shared memory as float32.
+//   OUT_FAST  the weight is contiguous along the outputs (w_js == 1).  128 threads = 16 groups of 8; a group covers 64
+//             outputs of one input row (8 per thread), the groups take the input rows 16 apart; sums meet by shuffles
+//             inside a warp (4 groups) and through shared memory across the 4 warps.
+//   else      the weight is contiguous along the inputs (w_is == 1).  A warp owns an output at a time, a lane 8
+//             consecutive inputs per step of 256; sums meet in a shuffle reduction.
+constexpr int kSmallTokens = 8;
+template <bool OUT_FAST>
+__global__ void __launch_bounds__(128) head_linear_small_kernel(
+    const __nv_bfloat16 * __restrict__ in, long long ld_in, int in_hs, const __nv_bfloat16 * __restrict__ w, long long w_hs,
+    long long w_stride, __nv_bfloat16 * __restrict__ out, long long ld_out, int out_hs, int N, int n_in, int n_out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float xin[];            // [kSmallTokens][n_in], then (OUT_FAST) [4][kSmallTokens][64]
+    const int h = blockIdx.y;
+    for (int e = threadIdx.x; e < kSmallTokens * n_in; e += blockDim.x) {
+        const int t = e / n_in, i = e - t * n_in;
+        xin[e] = t < N ? to_f32(in[(size_t) t * ld_in + (size_t) h * in_hs + i]) : 0.0f;
+    }
+    __syncthreads();
+    const __nv_bfloat16 * wh = w + (size_t) h * w_hs;
+    if (OUT_FAST) {
+        const int ct = threadIdx.x & 7, ig = threadIdx.x >> 3, warp = threadIdx.x >> 5;
+        const int j = blockIdx.x * 64 + ct * 8;
+        float acc[kSmallTokens][8];
+#pragma unroll
+        for (int t = 0; t < kSmallTokens; t++)
+#pragma unroll
+            for (int c = 0; c < 8; c++) acc[t][c] = 0.0f;
+        if (j < n_out) {                                     // n_out is a multiple of 8: a thread's 8 outputs are in or out together
+#pragma unroll 8
+            for (int i = ig; i < n_in; i += 16) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(wh + (size_t) i * w_stride + j);
+                float wv[8];
+                unpack8(raw, wv);
+#pragma unroll
+                for (int t = 0; t < kSmallTokens; t++) {
+                    const float x = xin[t * n_in + i];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) acc[t][c] = fmaf(x, wv[c], acc[t][c]);
+                }
+            }
+        }
+        float * red = xin + kSmallTokens * n_in;             // [4 warps][kSmallTokens][64]
+#pragma unroll
+        for (int t = 0; t < kSmallTokens; t++)
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float v = acc[t][c];
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if ((threadIdx.x & 31) < 8) red[(warp * kSmallTokens + t) * 64 + ct * 8 + c] = v;
+            }
+        __syncthreads();
+        for (int e = threadIdx.x; e < N * 64; e += blockDim.x) {
+            const int t = e >> 6, c = e & 63;
+            const int jo = blockIdx.x * 64 + c;
+            if (jo >= n_out) continue;
+            const float v = red[(0 * kSmallTokens + t) * 64 + c] + red[(1 * kSmallTokens + t) * 64 + c] +
+                            red[(2 * kSmallTokens + t) * 64 + c] + red[(3 * kSmallTokens + t) * 64 + c];
+            out[(size_t) t * ld_out + (size_t) h * out_hs + jo] = __float2bfloat16_rn(v);
+        }
+    } else {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int j = blockIdx.x * 8 + warp; j < min(n_out, (int) blockIdx.x * 8 + 8); j += 4) {
+            const __nv_bfloat16 * wj = wh + (size_t) j * w_stride;
+            float acc[kSmallTokens];
+#pragma unroll
+            for (int t = 0; t < kSmallTokens; t++) acc[t] = 0.0f;
+#pragma unroll 2
+            for (int i = lane * 8; i < n_in; i += 256) {     // n_in is a multiple of 8
+                const uint4 raw = *reinterpret_cast<const uint4 *>(wj + i);
+                float wv[8];
+                unpack8(raw, wv);
+#pragma unroll
+                for (int t = 0; t < kSmallTokens; t++) {
+                    const float4 x0 = *reinterpret_cast<const float4 *>(xin + t * n_in + i);
+                    const float4 x1 = *reinterpret_cast<const float4 *>(xin + t * n_in + i + 4);
+                    acc[t] += x0.x * wv[0] + x0.y * wv[1] + x0.z * wv[2] + x0.w * wv[3] + x1.x * wv[4] + x1.y * wv[5] + x1.z * wv[6] + x1.w * wv[7];
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kSmallTokens; t++) acc[t] = warp_sum(acc[t]);
+            if (lane == 0)
+                for (int t = 0; t < N; t++) out[(size_t) t * ld_out + (size_t) h * out_hs + j] = __float2bfloat16_rn(acc[t]);
+        }
+    }
+}
+
 template <typename A>
 __global__ void latent_attention_kernel(const A * __restrict__ q, const A * __restrict__ cache, A * __restrict__ out,
                                         const float * __restrict__ sink, const int * __restrict__ positions,
@@ -230,6 +321,27 @@ IIAN_API int iian_head_linear(const void * in, long long ld_in, int in_hs, const
         return iian_launch(head_linear_kernel<bf, float>, dim3(N, H), dim3(threads), smem, stream, (const bf *) in, ld_in, in_hs,
                            (const float *) w, w_hs, w_is, w_js, (bf *) out, ld_out, out_hs, N, H, n_in, n_out);
     return IIAN_ERR_DTYPE;
+}
+
+// The form for up to 8 tokens (bfloat16 activations and weights); w_is or w_js must be 1, the contiguous extent of the
+// weight a multiple of 8 and every row of it 16-byte aligned (else IIAN_ERR_SHAPE / IIAN_ERR_ALIGN: use the general form).
+IIAN_API int iian_head_linear_small(const void * in, long long ld_in, int in_hs, const void * w, long long w_hs, long long w_is,
+                                    long long w_js, void * out, long long ld_out, int out_hs, int N, int H, int n_in, int n_out,
+                                    cudaStream_t stream) {
+    if (N <= 0 || H <= 0 || n_out <= 0) return IIAN_OK;
+    if (N > kSmallTokens || n_in <= 0 || H > 65535 || (w_is != 1 && w_js != 1)) return IIAN_ERR_SHAPE;
+    typedef __nv_bfloat16 bf;
+    const bool out_fast = w_js == 1;
+    const long long stride = out_fast ? w_is : w_js;
+    if ((out_fast ? n_out : n_in) % 8 != 0) return IIAN_ERR_SHAPE;
+    if (((uintptr_t) w & 15) || stride % 8 != 0 || w_hs % 8 != 0) return IIAN_ERR_ALIGN;
+    const size_t smem = ((size_t) kSmallTokens * n_in + (out_fast ? 4 * kSmallTokens * 64 : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return IIAN_ERR_LIMIT;
+    if (out_fast)
+        return iian_launch(head_linear_small_kernel<true>, dim3((n_out + 63) / 64, H), dim3(128), smem, stream, (const bf *) in, ld_in,
+                           in_hs, (const bf *) w, w_hs, stride, (bf *) out, ld_out, out_hs, N, n_in, n_out);
+    return iian_launch(head_linear_small_kernel<false>, dim3((n_out + 7) / 8, H), dim3(128), smem, stream, (const bf *) in, ld_in,
+                       in_hs, (const bf *) w, w_hs, stride, (bf *) out, ld_out, out_hs, N, n_in, n_out);
 }
 
 // q: [N, H, width]; cache: [num_pages * page_size, width]; out: [N, H, rank]; sink: f32 [H] or null;

@@ -2,9 +2,9 @@
 // for decoded tokens alike.
 //
 // All heads of a token score the SAME cached rows (see latent_attention.cu), so the rows of one product are
-// (token, head) pairs: a CTA takes up to 32 of them from one sequence -- with 16 heads that is two tokens, in a decode
-// step all heads of the one token -- and walks the keys they can see in tiles of 64 that start at multiples of 64 of
-// the ABSOLUTE key position (the order of every sum depends on the row's own position only).  Per tile:
+// (token, head) pairs: a CTA takes up to 32 of them from one sequence (16 in the form for decoded tokens) -- with 16 heads that is two
+// tokens, in a decode step all heads of the one token -- and walks the keys they can see in tiles of 64 (32) that start
+// at multiples of the tile size of the ABSOLUTE key position (the order of every sum depends on the row's own position only).  Per tile:
 //   1. the tile's cache rows come by 16-byte cp.async through the block table into one of two shared-memory stages
 //      (rows past the newest key, or in a page that was given back, are zero-filled);
 //   2. S = Q K^T: each of the four warps takes 16 of the 64 keys for all rows (Q stays in shared memory; a cache row
@@ -13,15 +13,17 @@
 //      sink, sum 1) and forms P = exp(S - max) as its A operand;
 //   4. O += P V: each warp owns a quarter of the latent's columns (V is the front of the same cache rows, read
 //      transposed by ldmatrix), so the wide output (rank 512: 128 accumulators a thread for 32 rows) fits registers.
-// The keys may be cut into parts (gridDim.z) for steps with few rows; a part leaves unnormalised sums with its
-// maximum and denominator in scratch memory and a second kernel merges them.
+// The keys may be cut into parts (gridDim.z, up to 32) for steps with few rows; a part leaves unnormalised sums with
+// its maximum and denominator in scratch memory and a second kernel merges them.
 #include "common.cuh"
 
 namespace iian {
 
-constexpr int kRows = 32;          // (token, head) rows per CTA: two m16 tiles
-constexpr int kKeys = 64;          // keys per tile
 constexpr int kWarps = 4;
+// Two forms.  MT = 2, KEYS = 64: 32 rows a CTA and tiles of 64 keys, for prompts' portions (at the widths of real models one
+// CTA holds most of an SM's shared memory).  MT = 1, KEYS = 32: 16 rows and tiles of 32 keys, for decoded tokens: the
+// CTA needs under half the shared memory and half the registers, so two or more share an SM and one's waits on
+// shared and global memory are covered by the other's products.
 
 __device__ __forceinline__ void cp_async16(void * smem, const void * gmem, bool pred) {
     const unsigned s = (unsigned) __cvta_generic_to_shared(smem);
@@ -53,10 +55,10 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned *>(&v);
 }
 
-// NT: n8 tiles of the output a warp owns (rank = 32 * NT).
+// NT: n8 tiles of the output a warp owns (rank = 32 * NT); MT: m16 tiles of rows; KEYS: keys per tile (32 or 64).
 // q: [N, H, width]; cache: [num_pages * page_size, width]; out: [N, H, rank].
 // With gridDim.z > 1: part_o [N * H, parts, rank] f32 (unnormalised), part_ml [N * H, parts, 2] (maximum, denominator).
-template <int NT>
+template <int NT, int MT, int KEYS>
 __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
     const __nv_bfloat16 * __restrict__ q, const __nv_bfloat16 * __restrict__ cache, __nv_bfloat16 * __restrict__ out,
     float * __restrict__ part_o, float * __restrict__ part_ml, const float * __restrict__ sink,
@@ -65,6 +67,9 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
     pdl_wait();
     pdl_launch_dependents();
     constexpr int rank = 32 * NT;
+    constexpr int kRows = 16 * MT, kKeys = KEYS;
+    constexpr int NS = KEYS / 32;                         // n8 tiles of the scores a warp computes
+    constexpr int KB = KEYS / 16;                         // 16-key blocks of a tile
     const int s = blockIdx.y;
     const int q0 = cu_q[s], q_len = cu_q[s + 1] - q0;
     const int rows_total = q_len * H;
@@ -99,37 +104,41 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
         tile_hi = min(tile_hi, tile_lo + per - 1);
     }
 
-    // Q rows into shared memory (rows past n_rows are zero)
-    for (int i = tid; i < kRows * chunks; i += kWarps * 32) {
-        const int r = i / chunks, c = i - r * chunks;
+    // Q rows into shared memory (rows past n_rows are zero): a few threads a row, 16-byte chunks interleaved among them
+    {
+        constexpr int per = kWarps * 32 / kRows;
+        const int r = tid / per;
         const bool ok = r < n_rows;
-        const __nv_bfloat16 * src = q + ((size_t) (q0 + (row0 + (ok ? r : 0)) / H) * H + (row0 + (ok ? r : 0)) % H) * width + c * 8;
-        cp_async16(q_s + r * ldb + c * 16, src, ok);
+        const int R = row0 + (ok ? r : 0);
+        const __nv_bfloat16 * src = q + ((size_t) (q0 + R / H) * H + R % H) * width;
+        for (int c = tid % per; c < chunks; c += per) cp_async16(q_s + r * ldb + c * 16, src + c * 8, ok);
     }
     const int * bt = block_table + (size_t) s * max_blocks;
+    // a tile's cache rows: a few threads a row (one look-up in the block table each), chunks interleaved among them
     auto load_tile = [&](int tile, int stage) {
+        constexpr int per = kWarps * 32 / kKeys;
         unsigned char * dst = k_s + (size_t) stage * kKeys * ldb;
-        for (int i = tid; i < kKeys * chunks; i += kWarps * 32) {
-            const int r = i / chunks, c = i - r * chunks;
-            const int j = tile * kKeys + r;
-            bool ok = j <= hi_all && j >= 0;
-            size_t cell = 0;
-            if (ok) {
-                const int page = bt[j / page_size];
-                ok = page >= 0 && page < num_pages;
-                if (ok) cell = (size_t) page * page_size + (j % page_size);
-            }
-            cp_async16(dst + r * ldb + c * 16, cache + cell * width + c * 8, ok);
+        const int r = tid / per;
+        const int j = tile * kKeys + r;
+        bool ok = j <= hi_all && j >= 0;
+        size_t cell = 0;
+        if (ok) {
+            const int page = bt[j / page_size];
+            ok = page >= 0 && page < num_pages;
+            if (ok) cell = (size_t) page * page_size + (j % page_size);
         }
+        const __nv_bfloat16 * src = cache + cell * width;
+        unsigned char * drow = dst + r * ldb;
+        for (int c = tid % per; c < chunks; c += per) cp_async16(drow + c * 16, src + c * 8, ok);
     };
     if (tile_lo <= tile_hi) load_tile(tile_lo, 0);
     cp_async_commit();
 
     // running softmax state of the rows this thread sees in its fragments: m-tile mt, rows g and g + 8
-    float m_run[2][2], l_run[2][2];
-    int p_row[2][2], lo_row[2][2];
+    float m_run[MT][2], l_run[MT][2];
+    int p_row[MT][2], lo_row[MT][2];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int hh = 0; hh < 2; hh++) {
             const int r = mt * 16 + g + hh * 8;
@@ -141,9 +150,9 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
             m_run[mt][hh] = opens ? sink[R % H] : -INFINITY;
             l_run[mt][hh] = opens ? 1.0f : 0.0f;
         }
-    float o_acc[2][NT][4];
+    float o_acc[MT][NT][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -157,51 +166,52 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
         if (tile + 1 <= tile_hi) load_tile(tile + 1, stage ^ 1);      // arrives while this tile is worked on
         cp_async_commit();
         const unsigned char * kt = k_s + (size_t) stage * kKeys * ldb;
-        // ---- S[:, 16 warp .. 16 warp + 16) ----
-        float sc[2][2][4];
+        // ---- S[:, this warp's quarter of the tile's keys] ----
+        float sc[MT][NS][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
+            for (int nt = 0; nt < NS; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) sc[mt][nt][e] = 0.0f;
+#pragma unroll 4
         for (int ks = 0; ks < ksteps; ks++) {
-            unsigned a[2][4], b[2][2];
+            unsigned a[MT][4], b[NS][2];
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < MT; mt++)
                 ldmatrix_x4(a[mt], q_s + (mt * 16 + (lane & 15)) * ldb + (ks * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-                ldmatrix_x2(b[nt], kt + (warp * 16 + nt * 8 + (lane & 7)) * ldb + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+            for (int nt = 0; nt < NS; nt++)
+                ldmatrix_x2(b[nt], kt + (warp * (8 * NS) + nt * 8 + (lane & 7)) * ldb + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++) mma_bf16(sc[mt][nt], a[mt], b[nt]);
+                for (int nt = 0; nt < NS; nt++) mma_bf16(sc[mt][nt], a[mt], b[nt]);
         }
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
+            for (int nt = 0; nt < NS; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int hh = e >> 1;
-                    const int col = warp * 16 + nt * 8 + tq * 2 + (e & 1);
+                    const int col = warp * (8 * NS) + nt * 8 + tq * 2 + (e & 1);
                     const int j = tile * kKeys + col;
                     const bool vis = j <= p_row[mt][hh] && j >= lo_row[mt][hh] && j < ctx;
                     s_s[(mt * 16 + g + hh * 8) * lds + col] = vis ? sc[mt][nt][e] * scale : -INFINITY;
                 }
         __syncthreads();
-        // ---- softmax over the 64 keys of the tile, per row (every warp does all rows) ----
-        unsigned pa[2][4][4];                              // P as A fragments: [m-tile][16-key block][4]
+        // ---- softmax over the keys of the tile, per row (every warp does all rows) ----
+        unsigned pa[MT][KB][4];                            // P as A fragments: [m-tile][16-key block][4]
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
-            float v[2][16];
+        for (int mt = 0; mt < MT; mt++) {
+            float v[2][4 * KB];
             float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int hh = 0; hh < 2; hh++) {
                 const float * srow = s_s + (mt * 16 + g + hh * 8) * lds;
 #pragma unroll
-                for (int kb = 0; kb < 4; kb++) {
+                for (int kb = 0; kb < KB; kb++) {
                     const float2 x0 = *reinterpret_cast<const float2 *>(srow + kb * 16 + tq * 2);
                     const float2 x1 = *reinterpret_cast<const float2 *>(srow + kb * 16 + 8 + tq * 2);
                     v[hh][kb * 4 + 0] = x0.x; v[hh][kb * 4 + 1] = x0.y; v[hh][kb * 4 + 2] = x1.x; v[hh][kb * 4 + 3] = x1.y;
@@ -216,7 +226,7 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
                 const float corr = m_run[mt][hh] == -INFINITY ? 0.0f : __expf(m_run[mt][hh] - m_new);
                 float psum = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
+                for (int i = 0; i < 4 * KB; i++) {
                     const float p = m_new == -INFINITY ? 0.0f : __expf(v[hh][i] - m_new);
                     v[hh][i] = p;
                     psum += p;
@@ -232,7 +242,7 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
                 }
             }
 #pragma unroll
-            for (int kb = 0; kb < 4; kb++) {
+            for (int kb = 0; kb < KB; kb++) {
                 pa[mt][kb][0] = pack_bf16(v[0][kb * 4 + 0], v[0][kb * 4 + 1]);     // row g,     keys 2 tq, 2 tq + 1
                 pa[mt][kb][1] = pack_bf16(v[1][kb * 4 + 0], v[1][kb * 4 + 1]);     // row g + 8
                 pa[mt][kb][2] = pack_bf16(v[0][kb * 4 + 2], v[0][kb * 4 + 3]);     // row g,     keys 8 + 2 tq, ...
@@ -241,20 +251,20 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
         }
         // ---- O[:, warp's columns] += P V ----
 #pragma unroll
-        for (int kb = 0; kb < 4; kb++)
+        for (int kb = 0; kb < KB; kb++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 unsigned b[2];
                 ldmatrix_x2_trans(b, kt + (kb * 16 + (lane & 15)) * ldb + (warp * (rank / 4) + nt * 8) * 2);
 #pragma unroll
-                for (int mt = 0; mt < 2; mt++) mma_bf16(o_acc[mt][nt], pa[mt][kb], b);
+                for (int mt = 0; mt < MT; mt++) mma_bf16(o_acc[mt][nt], pa[mt][kb], b);
             }
     }
     cp_async_wait<0>();
 
     // ---- write ----
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int hh = 0; hh < 2; hh++) {
             const int r = mt * 16 + g + hh * 8;
@@ -290,26 +300,35 @@ __global__ void latent_merge_kernel(const float * __restrict__ part_o, const flo
                                     int rank) {
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ float wz[64];                  // the weight of every part: exp(m_z - m) / l
     const size_t row = blockIdx.x;
     if (seq_of_token[row / H] < 0) {
         for (int c = threadIdx.x; c < rank; c += blockDim.x) out[row * rank + c] = __float2bfloat16_rn(0.0f);
         return;
     }
-    float m = -INFINITY;
-    for (int z = 0; z < parts; z++) m = fmaxf(m, part_ml[(row * parts + z) * 2]);
-    float l = 0.0f;
-    for (int z = 0; z < parts; z++) {
-        const float mz = part_ml[(row * parts + z) * 2];
-        if (mz != -INFINITY) l += part_ml[(row * parts + z) * 2 + 1] * __expf(mz - m);
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
-        float acc = 0.0f;
-        for (int z = 0; z < parts; z++) {
-            const float mz = part_ml[(row * parts + z) * 2];
-            if (mz != -INFINITY) acc += part_o[(row * parts + z) * rank + c] * __expf(mz - m);
+    if (threadIdx.x < 32) {
+        const int z = threadIdx.x;
+        const float mz = z < parts ? part_ml[(row * parts + z) * 2] : -INFINITY;
+        const float lz = z < parts ? part_ml[(row * parts + z) * 2 + 1] : 0.0f;
+        const float m = warp_max(mz);
+        const float e = mz == -INFINITY ? 0.0f : __expf(mz - m);
+        float l = lz * e;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {     // in the order of the parts: a prefix-style sum keeps z ascending pairs together
+            l += __shfl_xor_sync(0xffffffffu, l, o);
         }
-        out[row * rank + c] = __float2bfloat16_rn(acc * inv);
+        wz[z] = l > 0.0f ? e / l : 0.0f;
+    }
+    __syncthreads();
+    const float * po = part_o + row * parts * rank;
+    for (int c = threadIdx.x * 2; c < rank; c += blockDim.x * 2) {
+        float a0 = 0.0f, a1 = 0.0f;
+        for (int z = 0; z < parts; z++) {
+            const float2 v = *reinterpret_cast<const float2 *>(po + (size_t) z * rank + c);
+            a0 = fmaf(v.x, wz[z], a0);
+            a1 = fmaf(v.y, wz[z], a1);
+        }
+        *reinterpret_cast<unsigned *>(out + row * rank + c) = pack_bf16(a0, a1);
     }
 }
 
@@ -317,33 +336,33 @@ __global__ void latent_merge_kernel(const float * __restrict__ part_o, const flo
 
 using namespace iian;
 
-static size_t latent_mma_smem(int width) {
+static size_t latent_mma_smem(int width, int rows, int keys) {
     const size_t ldb = (size_t) width * 2 + 16;
-    return kRows * ldb + 2 * kKeys * ldb + (size_t) kRows * (kKeys + 4) * sizeof(float);
+    return rows * ldb + 2 * keys * ldb + (size_t) rows * (keys + 4) * sizeof(float);
 }
 
 // 0 if the sizes are ones this kernel takes
 IIAN_API int iian_latent_attention_mma_ok(int rank, int width, int H) {
     if (rank != 64 && rank != 128 && rank != 256 && rank != 512) return IIAN_ERR_SHAPE;
     if (width < rank || width % 16 != 0 || H <= 0) return IIAN_ERR_SHAPE;
-    if (latent_mma_smem(width) > 220 * 1024) return IIAN_ERR_LIMIT;
+    if (latent_mma_smem(width, 32, 64) > 220 * 1024) return IIAN_ERR_LIMIT;
     return IIAN_OK;
 }
 
-template <int NT>
+template <int NT, int MT, int KEYS>
 static int launch_latent_mma(const void * q, const void * cache, void * out, float * part_o, float * part_ml, const float * sink,
                              const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks, int S, int max_q_len,
                              int H, int width, int page_size, int num_pages, float scale, int window, int parts, cudaStream_t stream) {
-    const size_t smem = latent_mma_smem(width);
+    const size_t smem = latent_mma_smem(width, 16 * MT, KEYS);
     static size_t attr_done = 0;
     if (smem > attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT, MT, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         attr_done = smem;
     }
-    const long long tiles = ((long long) max_q_len * H + kRows - 1) / kRows;
-    if (tiles > 2147483647LL || S > 65535 || parts > 65535) return IIAN_ERR_LIMIT;
-    return iian_launch(latent_attention_mma_kernel<NT>, dim3((unsigned) tiles, S, parts), dim3(kWarps * 32), smem, stream,
+    const long long tiles = ((long long) max_q_len * H + 16 * MT - 1) / (16 * MT);
+    if (tiles > 2147483647LL || S > 65535 || parts > 32) return IIAN_ERR_LIMIT;
+    return iian_launch(latent_attention_mma_kernel<NT, MT, KEYS>, dim3((unsigned) tiles, S, parts), dim3(kWarps * 32), smem, stream,
                        (const __nv_bfloat16 *) q, (const __nv_bfloat16 *) cache, (__nv_bfloat16 *) out, part_o, part_ml, sink, cu_q,
                        ctx_len, block_table, max_blocks, H, width, page_size, num_pages, scale, window);
 }
@@ -360,9 +379,13 @@ IIAN_API int iian_latent_attention_mma(const void * q, const void * cache, void 
     if (code != IIAN_OK) return code;
     if (parts < 1 || (parts > 1 && (part_o == nullptr || part_ml == nullptr || seq_of_token == nullptr))) return IIAN_ERR_SHAPE;
     if (((uintptr_t) q & 15) || ((uintptr_t) cache & 15) || ((uintptr_t) out & 3)) return IIAN_ERR_ALIGN;
+    // decoded tokens (and any step whose sequences bring at most 16 rows): the form of which several CTAs share an SM
+    const bool small = (long long) max_q_len * H <= 16 || max_q_len == 1;
 #define IIAN_LAT(NTV)                                                                                                        \
-    code = launch_latent_mma<NTV>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, max_q_len, H, \
-                                  width, page_size, num_pages, scale, window, parts, stream)
+    code = small ? launch_latent_mma<NTV, 1, 32>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                 max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)    \
+                 : launch_latent_mma<NTV, 2, 64>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                 max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)
     if (rank == 64) IIAN_LAT(2);
     else if (rank == 128) IIAN_LAT(4);
     else if (rank == 256) IIAN_LAT(8);

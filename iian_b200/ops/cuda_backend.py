@@ -941,6 +941,8 @@ class CudaKernels:
                   _code(qd, "projected rows"), n, num_heads, dim, rot, rank, rot_dims if inv_freq is not None else 0, eps,
                   n_cells, _stream()), "latent_prep")
 
+    HEAD_LINEAR_FAST = os.environ.get("IIAN_HEAD_LINEAR_FAST", "1") not in ("0", "false", "off")
+
     def head_linear(self, inp: torch.Tensor, in_off: int, in_head_stride: int, w: torch.Tensor, w_head_stride: int, w_in_stride: int,
                     w_out_stride: int, out: torch.Tensor, out_off: int, out_head_stride: int, *, num_heads: int, n_in: int,
                     n_out: int) -> None:
@@ -950,11 +952,33 @@ class CudaKernels:
         ip, ld_in = self._rows(inp, "head_linear in")
         op, ld_out = self._rows(out, "head_linear out")
         es = inp.element_size()
+        if out.dtype != inp.dtype:
+            raise KernelError("head_linear: in and out must share the activation dtype")
+        if n == 0:
+            return
+        if inp.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and self.HEAD_LINEAR_FAST:
+            # bfloat16: up to 8 tokens a form that reads the weights once; beyond, the library's batched product on
+            # strided views (as plain products of that many rows go to the library)
+            contiguous, stride = (n_out, w_in_stride) if w_out_stride == 1 else (n_in, w_out_stride)
+            if (n <= 8 and (w_in_stride == 1 or w_out_stride == 1) and n_in * 32 + 8192 <= 48 * 1024 and contiguous % 8 == 0
+                    and stride % 8 == 0 and w_head_stride % 8 == 0 and w.data_ptr() % 16 == 0):
+                fn = _fn("latent_attention", "iian_head_linear_small",
+                         [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_int,
+                          c_int, c_int, c_int, c_int, c_void_p])
+                _check(fn(ip + in_off * es, ld_in, in_head_stride, _cuda(w, "head_linear w"), w_head_stride, w_in_stride,
+                          w_out_stride, op + out_off * es, ld_out, out_head_stride, n, num_heads, n_in, n_out, _stream()),
+                       "head_linear_small")
+                return
+            if n > 8:
+                a = torch.as_strided(inp, (num_heads, n, n_in), (in_head_stride, ld_in, 1), inp.storage_offset() + in_off)
+                b = torch.as_strided(w, (num_heads, n_in, n_out), (w_head_stride, w_in_stride, w_out_stride), w.storage_offset())
+                c = torch.as_strided(out, (num_heads, n, n_out), (out_head_stride, ld_out, 1), out.storage_offset() + out_off)
+                torch.bmm(a, b, out=c)
+                LAUNCHES_BY_ENTRY["library_gemm"] = LAUNCHES_BY_ENTRY.get("library_gemm", 0) + 1
+                return
         fn = _fn("latent_attention", "iian_head_linear",
                  [c_void_p, c_longlong, c_int, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_int,
                   c_int, c_int, c_int, c_int, c_int, c_void_p])
-        if out.dtype != inp.dtype:
-            raise KernelError("head_linear: in and out must share the activation dtype")
         _check(fn(ip + in_off * es, ld_in, in_head_stride, _cuda(w, "head_linear w"), _code(w, "head_linear w"), w_head_stride,
                   w_in_stride, w_out_stride, op + out_off * es, ld_out, out_head_stride, _code(inp, "head_linear in"), n,
                   num_heads, n_in, n_out, _stream()), "head_linear")
@@ -987,13 +1011,15 @@ class CudaKernels:
         return fn(rank, q_cat.shape[2], q_cat.shape[1]) == 0
 
     def latent_attention_parts(self, num_seqs: int, max_q_len: int, num_heads: int, max_ctx: int, window: Optional[int]) -> int:
-        """Into how many parts the keys are cut so that a step with few rows still fills the GPU: a CTA takes 32
-        (token, head) rows of one sequence and holds most of an SM's shared memory at the widths of real models, so
-        the aim is one CTA per SM, each with at least two key tiles of 64."""
-        ctas = max(1, num_seqs * (-(-max_q_len * num_heads // 32)))
+        """Into how many parts the keys are cut so that a step with few rows still fills the GPU.  Decoded tokens run in
+        the kernel's small form (16 rows a CTA, tiles of 32 keys, two CTAs an SM at the widths of real models), portions
+        of prompts in the large one (32 rows, tiles of 64 keys, one CTA an SM); a part keeps at least four (two) tiles."""
+        small = max_q_len == 1 or max_q_len * num_heads <= 16
+        rows, tile, per_sm, least = (16, 32, 2, 4) if small else (32, 64, 1, 2)
+        ctas = max(1, num_seqs * (-(-max_q_len * num_heads // rows)))
         keys = min(max_ctx, window + max_q_len) if window else max_ctx
-        tiles = -(-keys // 64) + 1
-        return max(1, min(self.sm_count() // ctas, tiles // 2, 32))
+        tiles = -(-keys // tile) + 1
+        return max(1, min(per_sm * self.sm_count() // ctas, tiles // least, 32))
 
     def latent_attention_mma(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, out: torch.Tensor, sink: Optional[torch.Tensor],
                              meta, *, num_heads: int, rank: int, scale: float, window: Optional[int],

@@ -218,18 +218,23 @@ def test_latent_prep_and_head_products(dtype):
     untouched = [s for s in range(64) if s not in slots.tolist()]
     assert float(flat[untouched].abs().max()) == 0.0
     close(q_cat[..., rank:], qr, dtype, "rotated query parts", rel16=6e-3)
+    # the per-head products: up to 8 tokens and more (in bfloat16 these are different kernels), both orientations
     uk = (torch.randn(heads * dim, rank, generator=g) * 0.3).to(DT[dtype])
-    K().head_linear(qd.to(DEV), q_off, dim + rot, uk.to(DEV), dim * rank, rank, 1, q_cat.view(n, heads * width), 0, width,
-                    num_heads=heads, n_in=dim, n_out=rank)
-    want = torch.einsum("thd,hdr->thr", q[..., :dim], uk.double().view(heads, dim, rank))
-    close(q_cat[..., :rank], want, dtype, "query moved into latent space")
-    close(q_cat[..., rank:], qr, dtype, "rotated query parts stay", rel16=6e-3)
-    lat = torch.randn(n, heads * rank, generator=g).to(DT[dtype])
     uv = (torch.randn(heads * vdim, rank, generator=g) * 0.3).to(DT[dtype])
-    o = torch.empty(n, heads * vdim, device=DEV, dtype=DT[dtype])
-    K().head_linear(lat.to(DEV), 0, rank, uv.to(DEV), vdim * rank, 1, rank, o, 0, vdim, num_heads=heads, n_in=rank, n_out=vdim)
-    want = torch.einsum("thr,hvr->thv", lat.double().view(n, heads, rank), uv.double().view(heads, vdim, rank))
-    close(o.view(n, heads, vdim), want, dtype, "values lifted per head")
+    for nn in (n, 1, 8, 9, 70):
+        qd2 = torch.randn(nn, q_off + heads * (dim + rot) + 3, generator=g).to(DT[dtype])
+        q2 = qd2.double()[:, q_off:q_off + heads * (dim + rot)].view(nn, heads, dim + rot)
+        q_cat2 = torch.full((nn, heads, width), 7.0, device=DEV, dtype=DT[dtype])
+        K().head_linear(qd2.to(DEV), q_off, dim + rot, uk.to(DEV), dim * rank, rank, 1, q_cat2.view(nn, heads * width), 0, width,
+                        num_heads=heads, n_in=dim, n_out=rank)
+        want = torch.einsum("thd,hdr->thr", q2[..., :dim], uk.double().view(heads, dim, rank))
+        close(q_cat2[..., :rank], want, dtype, f"query moved into latent space, {nn} tokens")
+        assert float((q_cat2[..., rank:].float() - 7.0).abs().max()) == 0.0, "the rotated parts behind it were touched"
+        lat = torch.randn(nn, heads * rank, generator=g).to(DT[dtype])
+        o = torch.empty(nn, heads * vdim, device=DEV, dtype=DT[dtype])
+        K().head_linear(lat.to(DEV), 0, rank, uv.to(DEV), vdim * rank, 1, rank, o, 0, vdim, num_heads=heads, n_in=rank, n_out=vdim)
+        want = torch.einsum("thr,hvr->thv", lat.double().view(nn, heads, rank), uv.double().view(heads, vdim, rank))
+        close(o.view(nn, heads, vdim), want, dtype, f"values lifted per head, {nn} tokens")
 
 
 # ---- routed experts -----------------------------------------------------------------------------------
