@@ -58,7 +58,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // NT: n8 tiles of the output a warp owns (rank = 32 * NT); MT: m16 tiles of rows; KEYS: keys per tile (32 or 64).
 // q: [N, H, width]; cache: [num_pages * page_size, width]; out: [N, H, rank].
 // With gridDim.z > 1: part_o [N * H, parts, rank] f32 (unnormalised), part_ml [N * H, parts, 2] (maximum, denominator).
-template <int NT, int MT, int KEYS>
+template <int NT, int MT, int KEYS, int STAGES>
 __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
     const __nv_bfloat16 * __restrict__ q, const __nv_bfloat16 * __restrict__ cache, __nv_bfloat16 * __restrict__ out,
     float * __restrict__ part_o, float * __restrict__ part_ml, const float * __restrict__ sink,
@@ -84,8 +84,8 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int ldb = width * 2 + 16;                        // bytes per padded row: rows 4 banks apart
     unsigned char * q_s = smem_raw;                        // [kRows][ldb]
-    unsigned char * k_s = q_s + kRows * ldb;               // [2][kKeys][ldb]
-    float * s_s = reinterpret_cast<float *>(k_s + 2 * kKeys * ldb);      // [kRows][kKeys + 4]
+    unsigned char * k_s = q_s + kRows * ldb;               // [STAGES][kKeys][ldb]
+    float * s_s = reinterpret_cast<float *>(k_s + STAGES * kKeys * ldb);      // [kRows][kKeys + 4]
     constexpr int lds = kKeys + 4;
     const int chunks = width / 8;                          // 16-byte chunks per row
 
@@ -160,11 +160,18 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(
 
     const int ksteps = width / 16;
     for (int tile = tile_lo; tile <= tile_hi; tile++) {
-        const int stage = (tile - tile_lo) & 1;
+        const int stage = STAGES == 2 ? (tile - tile_lo) & 1 : 0;
+        if (STAGES == 1 && tile > tile_lo) {               // one stage: the next tile may come only when all are done with this one
+            __syncthreads();
+            load_tile(tile, 0);
+            cp_async_commit();
+        }
         cp_async_wait<0>();
         __syncthreads();                                   // this tile (and Q) are in shared memory for all; everyone is done with the last tile
-        if (tile + 1 <= tile_hi) load_tile(tile + 1, stage ^ 1);      // arrives while this tile is worked on
-        cp_async_commit();
+        if (STAGES == 2) {
+            if (tile + 1 <= tile_hi) load_tile(tile + 1, stage ^ 1);      // arrives while this tile is worked on
+            cp_async_commit();
+        }
         const unsigned char * kt = k_s + (size_t) stage * kKeys * ldb;
         // ---- S[:, this warp's quarter of the tile's keys] ----
         float sc[MT][NS][4];
@@ -336,9 +343,18 @@ __global__ void latent_merge_kernel(const float * __restrict__ part_o, const flo
 
 using namespace iian;
 
-static size_t latent_mma_smem(int width, int rows, int keys) {
+static size_t latent_mma_smem(int width, int rows, int keys, int stages = 2) {
     const size_t ldb = (size_t) width * 2 + 16;
-    return rows * ldb + 2 * keys * ldb + (size_t) rows * (keys + 4) * sizeof(float);
+    return rows * ldb + stages * keys * ldb + (size_t) rows * (keys + 4) * sizeof(float);
+}
+
+// the form for prompts' portions: 0 = 32 rows, tiles of 64 keys in two stages (one CTA an SM at width 576);
+// 1 = 32 rows, tiles of 32 keys in one stage (two CTAs an SM, each covers the other's loads)
+static int g_large_form = 1;
+IIAN_API int iian_latent_attention_large_form(int form) {
+    if (form != 0 && form != 1) return IIAN_ERR_SHAPE;
+    g_large_form = form;
+    return IIAN_OK;
 }
 
 // 0 if the sizes are ones this kernel takes
@@ -349,20 +365,20 @@ IIAN_API int iian_latent_attention_mma_ok(int rank, int width, int H) {
     return IIAN_OK;
 }
 
-template <int NT, int MT, int KEYS>
+template <int NT, int MT, int KEYS, int STAGES>
 static int launch_latent_mma(const void * q, const void * cache, void * out, float * part_o, float * part_ml, const float * sink,
                              const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks, int S, int max_q_len,
                              int H, int width, int page_size, int num_pages, float scale, int window, int parts, cudaStream_t stream) {
-    const size_t smem = latent_mma_smem(width, 16 * MT, KEYS);
+    const size_t smem = latent_mma_smem(width, 16 * MT, KEYS, STAGES);
     static size_t attr_done = 0;
     if (smem > attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT, MT, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT, MT, KEYS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         attr_done = smem;
     }
     const long long tiles = ((long long) max_q_len * H + 16 * MT - 1) / (16 * MT);
     if (tiles > 2147483647LL || S > 65535 || parts > 32) return IIAN_ERR_LIMIT;
-    return iian_launch(latent_attention_mma_kernel<NT, MT, KEYS>, dim3((unsigned) tiles, S, parts), dim3(kWarps * 32), smem, stream,
+    return iian_launch(latent_attention_mma_kernel<NT, MT, KEYS, STAGES>, dim3((unsigned) tiles, S, parts), dim3(kWarps * 32), smem, stream,
                        (const __nv_bfloat16 *) q, (const __nv_bfloat16 *) cache, (__nv_bfloat16 *) out, part_o, part_ml, sink, cu_q,
                        ctx_len, block_table, max_blocks, H, width, page_size, num_pages, scale, window);
 }
@@ -382,10 +398,12 @@ IIAN_API int iian_latent_attention_mma(const void * q, const void * cache, void 
     // decoded tokens (and any step whose sequences bring at most 16 rows): the form of which several CTAs share an SM
     const bool small = (long long) max_q_len * H <= 16 || max_q_len == 1;
 #define IIAN_LAT(NTV)                                                                                                        \
-    code = small ? launch_latent_mma<NTV, 1, 32>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
-                                                 max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)    \
-                 : launch_latent_mma<NTV, 2, 64>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
-                                                 max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)
+    code = small ? launch_latent_mma<NTV, 1, 32, 2>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                    max_q_len, H, width, page_size, num_pages, scale, window, parts, stream) \
+         : g_large_form == 1 ? launch_latent_mma<NTV, 2, 32, 1>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                    max_q_len, H, width, page_size, num_pages, scale, window, parts, stream) \
+                 : launch_latent_mma<NTV, 2, 64, 2>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                    max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)
     if (rank == 64) IIAN_LAT(2);
     else if (rank == 128) IIAN_LAT(4);
     else if (rank == 256) IIAN_LAT(8);

@@ -1003,6 +1003,9 @@ class CudaKernels:
 
     # the same on the tensor cores (csrc/latent_attention_mma.cu): bfloat16, rank 64 / 128 / 256 / 512, rot a multiple of 16
     LATENT_MMA = os.environ.get("IIAN_LATENT_MMA", "1") not in ("0", "false", "off")
+    # the form for prompts' portions: 1 = tiles of 32 keys in one stage, two CTAs an SM; 0 = tiles of 64 keys in two stages
+    LATENT_LARGE_FORM = int(os.environ.get("IIAN_LATENT_LARGE_FORM", "1"))
+    _latent_form_set = None
 
     def latent_attention_mma_ok(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, rank: int) -> bool:
         if not self.LATENT_MMA or q_cat.dtype != torch.bfloat16 or cache_rows.dtype != torch.bfloat16:
@@ -1012,10 +1015,10 @@ class CudaKernels:
 
     def latent_attention_parts(self, num_seqs: int, max_q_len: int, num_heads: int, max_ctx: int, window: Optional[int]) -> int:
         """Into how many parts the keys are cut so that a step with few rows still fills the GPU.  Decoded tokens run in
-        the kernel's small form (16 rows a CTA, tiles of 32 keys, two CTAs an SM at the widths of real models), portions
-        of prompts in the large one (32 rows, tiles of 64 keys, one CTA an SM); a part keeps at least four (two) tiles."""
+        the kernel's small form (16 rows a CTA, tiles of 32 keys), portions of prompts in the large one (32 rows); of
+        either, two CTAs share an SM at the widths of real models; a part keeps at least four tiles."""
         small = max_q_len == 1 or max_q_len * num_heads <= 16
-        rows, tile, per_sm, least = (16, 32, 2, 4) if small else (32, 64, 1, 2)
+        rows, tile, per_sm, least = (16, 32, 2, 4) if small else (32, 32 if self.LATENT_LARGE_FORM else 64, 2 if self.LATENT_LARGE_FORM else 1, 4)
         ctas = max(1, num_seqs * (-(-max_q_len * num_heads // rows)))
         keys = min(max_ctx, window + max_q_len) if window else max_ctx
         tiles = -(-keys // tile) + 1
@@ -1029,6 +1032,10 @@ class CudaKernels:
             raise KernelError(f"latent_attention_mma: q {tuple(q_cat.shape)}, cache {tuple(cache_rows.shape)}, out {tuple(out.shape)} do not fit")
         if parts is None:
             parts = self.latent_attention_parts(meta.num_seqs, meta.max_q_len, h, meta.max_ctx, window)
+        if CudaKernels._latent_form_set != self.LATENT_LARGE_FORM:
+            if _fn("latent_attention_mma", "iian_latent_attention_large_form", [c_int])(self.LATENT_LARGE_FORM) != 0:
+                raise KernelError("IIAN_LATENT_LARGE_FORM takes 0 or 1")
+            CudaKernels._latent_form_set = self.LATENT_LARGE_FORM
         part_o = part_ml = 0
         if parts > 1:
             scratch = self.attention_scratch(q_cat.device, n * h * parts * (rank + 2))
