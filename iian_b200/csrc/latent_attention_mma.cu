@@ -356,6 +356,13 @@ IIAN_API int iian_latent_attention_large_form(int form) {
     g_large_form = form;
     return IIAN_OK;
 }
+// the form for decoded tokens (16 rows, tiles of 32 keys): 0 = two stages (two CTAs an SM at width 576), 1 = one stage (three)
+static int g_small_form = 0;
+IIAN_API int iian_latent_attention_small_form(int form) {
+    if (form != 0 && form != 1) return IIAN_ERR_SHAPE;
+    g_small_form = form;
+    return IIAN_OK;
+}
 
 // 0 if the sizes are ones this kernel takes
 IIAN_API int iian_latent_attention_mma_ok(int rank, int width, int H) {
@@ -398,8 +405,11 @@ IIAN_API int iian_latent_attention_mma(const void * q, const void * cache, void 
     // decoded tokens (and any step whose sequences bring at most 16 rows): the form of which several CTAs share an SM
     const bool small = (long long) max_q_len * H <= 16 || max_q_len == 1;
 #define IIAN_LAT(NTV)                                                                                                        \
-    code = small ? launch_latent_mma<NTV, 1, 32, 2>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
-                                                    max_q_len, H, width, page_size, num_pages, scale, window, parts, stream) \
+    code = small ? (g_small_form == 1                                                                                           \
+                    ? launch_latent_mma<NTV, 1, 32, 1>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                       max_q_len, H, width, page_size, num_pages, scale, window, parts, stream) \
+                    : launch_latent_mma<NTV, 1, 32, 2>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
+                                                       max_q_len, H, width, page_size, num_pages, scale, window, parts, stream)) \
          : g_large_form == 1 ? launch_latent_mma<NTV, 2, 32, 1>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \
                                                     max_q_len, H, width, page_size, num_pages, scale, window, parts, stream) \
                  : launch_latent_mma<NTV, 2, 64, 2>(q, cache, out, part_o, part_ml, sink, cu_q, ctx_len, block_table, max_blocks, S, \

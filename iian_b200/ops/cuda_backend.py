@@ -1005,6 +1005,8 @@ class CudaKernels:
     LATENT_MMA = os.environ.get("IIAN_LATENT_MMA", "1") not in ("0", "false", "off")
     # the form for prompts' portions: 1 = tiles of 32 keys in one stage, two CTAs an SM; 0 = tiles of 64 keys in two stages
     LATENT_LARGE_FORM = int(os.environ.get("IIAN_LATENT_LARGE_FORM", "1"))
+    # the form for decoded tokens: 0 = two stages, two CTAs an SM; 1 = one stage, three CTAs an SM
+    LATENT_SMALL_FORM = int(os.environ.get("IIAN_LATENT_SMALL_FORM", "0"))
     _latent_form_set = None
 
     def latent_attention_mma_ok(self, q_cat: torch.Tensor, cache_rows: torch.Tensor, rank: int) -> bool:
@@ -1018,7 +1020,7 @@ class CudaKernels:
         the kernel's small form (16 rows a CTA, tiles of 32 keys), portions of prompts in the large one (32 rows); of
         either, two CTAs share an SM at the widths of real models; a part keeps at least four tiles."""
         small = max_q_len == 1 or max_q_len * num_heads <= 16
-        rows, tile, per_sm, least = (16, 32, 2, 4) if small else (32, 32 if self.LATENT_LARGE_FORM else 64, 2 if self.LATENT_LARGE_FORM else 1, 4)
+        rows, tile, per_sm, least = (16, 32, 3 if self.LATENT_SMALL_FORM else 2, 4) if small else (32, 32 if self.LATENT_LARGE_FORM else 64, 2 if self.LATENT_LARGE_FORM else 1, 4)
         ctas = max(1, num_seqs * (-(-max_q_len * num_heads // rows)))
         keys = min(max_ctx, window + max_q_len) if window else max_ctx
         tiles = -(-keys // tile) + 1
@@ -1032,10 +1034,11 @@ class CudaKernels:
             raise KernelError(f"latent_attention_mma: q {tuple(q_cat.shape)}, cache {tuple(cache_rows.shape)}, out {tuple(out.shape)} do not fit")
         if parts is None:
             parts = self.latent_attention_parts(meta.num_seqs, meta.max_q_len, h, meta.max_ctx, window)
-        if CudaKernels._latent_form_set != self.LATENT_LARGE_FORM:
-            if _fn("latent_attention_mma", "iian_latent_attention_large_form", [c_int])(self.LATENT_LARGE_FORM) != 0:
-                raise KernelError("IIAN_LATENT_LARGE_FORM takes 0 or 1")
-            CudaKernels._latent_form_set = self.LATENT_LARGE_FORM
+        if CudaKernels._latent_form_set != (self.LATENT_LARGE_FORM, self.LATENT_SMALL_FORM):
+            if _fn("latent_attention_mma", "iian_latent_attention_large_form", [c_int])(self.LATENT_LARGE_FORM) != 0 \
+                    or _fn("latent_attention_mma", "iian_latent_attention_small_form", [c_int])(self.LATENT_SMALL_FORM) != 0:
+                raise KernelError("IIAN_LATENT_LARGE_FORM and IIAN_LATENT_SMALL_FORM take 0 or 1")
+            CudaKernels._latent_form_set = (self.LATENT_LARGE_FORM, self.LATENT_SMALL_FORM)
         part_o = part_ml = 0
         if parts > 1:
             scratch = self.attention_scratch(q_cat.device, n * h * parts * (rank + 2))

@@ -165,3 +165,21 @@ def test_greedy_generation_through_the_scheduler(cases):
             assert eng.generate(prompts, max_tokens=5, temperature=0.0) == want
         eng.cache.check_invariants()
         assert all(p.num_free == p.num_blocks for p in eng.cache.pools)
+
+
+def test_command_line_writes_and_loads_a_folder(tmp_path):
+    """``iian random-weights`` from a Galodra config.json, then the folder through the loader (names, shapes, the plug-in)."""
+    from iian_b200.cli.main import main as cli_main
+    from iian_b200.config.registry import load_model_config
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(CONFIGS["R"]))
+    out = tmp_path / "model"
+    assert cli_main(["random-weights", str(cfg_path), str(out), "--seed", "3"]) == 0
+    arch, cfg = load_model_config(str(out))
+    assert arch.name == "Galodra" and cfg == arch.load_config(CONFIGS["R"])
+    with ops.use_kernels(FakeKernels()):
+        model = Model.from_folder(str(out), "float32", "cpu")
+        rp = TraceReplayer(model, 64, 16, 2, native=False)
+        logits = rp.run_step({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": ["a"]})
+    want = plain.forward(*plain.load_folder(str(out)), [1, 2, 3])[-1]
+    assert (logits[0].double() - want).abs().max() < 2e-4
