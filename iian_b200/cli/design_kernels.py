@@ -3,9 +3,9 @@
     python -m iian_b200.cli.design_kernels            (or ``bench.py --design galodra --kernels``)
 
 A kernel is timed as a replayed CUDA graph of a few launches on different copies of its operands (which together exceed
-the L2), after one eager run, with a 256 MB buffer written before every replay; the median of several replays counts.
-Achieved bytes or flops are the
-algorithmic ones (what the operation has to read and write, or multiply) over that time, set against the measured copy
+the L2 wherever memory is the bound), after one eager run, with a 256 MB buffer written before every replay; the median
+of several replays counts (a graph of ONE short launch cannot read below some 16 us, hence several).  Achieved bytes or
+flops are the algorithmic ones (what the operation has to read and write, or multiply) over that time, set against the measured copy
 bandwidth and bfloat16 product peak.
 
 Pairs (width 2048, 16 heads; latent rank 512 + 64 rotated; Qwen3 side: 16 heads of 128 on 8 KV heads):
@@ -133,7 +133,7 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
     q2 = torch.randn(T, heads, hd, device=dev).to(bf) * 0.1
     o2 = torch.empty(T, heads * hd, device=dev, dtype=bf)
-    ms = _timed(lambda: k.paged_attention(q2, kc, vc, o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=window))
+    ms = _timed([lambda: k.paged_attention(q2, kc, vc, o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=window)] * 4)
     flop_row("prefill_attention_qwen3", ms, 4.0 * heads * hd * pairs)
 
     # ---- expert products beside the dense products of the same active size -------------------------------------------
@@ -179,8 +179,21 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
             else:
                 k.linear(h, wgu, gu)
                 k.swiglu(gu, a2, 8)
-        ms1 = _timed(dense_gate_up)
-        ms2 = _timed(lambda: k.linear(a2, wd, y2))
+        # at 8 tokens the weights are the traffic: three copies (207 MB) so that none waits in the L2
+        wgus = [wgu] + [wgu.clone() for _ in range(2 if n < 128 else 0)]
+        wds = [wd] + [wd.clone() for _ in range(5 if n < 128 else 0)]
+
+        def dense_gate_up_on(wm):
+            def run_():
+                if fused:
+                    k.linear_swiglu(h, wm, a2)
+                else:
+                    k.linear(h, wm, gu)
+                    k.swiglu(gu, a2, 8)
+            return run_
+        ms1 = _timed([dense_gate_up_on(wm) for wm in wgus] * (1 if n < 128 else 3))
+        ms2 = _timed([(lambda wm=wm: k.linear(a2, wm, y2)) for wm in wds] * (1 if n < 128 else 3))
+        del wgus, wds
         if n >= 128:
             flop_row(f"dense_gate_up_{n}", ms1, 2.0 * n * 2 * inter * width)
             flop_row(f"dense_down_{n}", ms2, 2.0 * n * inter * width)
@@ -196,28 +209,31 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     gate = torch.randn(n, width, device=dev).to(bf)
     gb, w, b = torch.zeros(width, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
     o32, o16 = torch.empty(n, width, device=dev), torch.empty(n, width, device=dev, dtype=bf)
-    ms = _timed(lambda: k.gated_add_layer_norm(x, sub, gate, gb, w, b, 2.0, 1e-6, o32, o16))
+    sets = [(x.clone(), sub.clone(), gate.clone(), torch.empty_like(o32), torch.empty_like(o16)) for _ in range(8)]
+    ms = _timed([(lambda t=t: k.gated_add_layer_norm(t[0], t[1], t[2], gb, w, b, 2.0, 1e-6, t[3], t[4])) for t in sets])
     mem_row("gated_sum_layer_norm", ms, n * width * (4 + 2 + 2 + 4 + 2))
-    ms = _timed(lambda: k.add_rms_norm(x, sub, w, 1e-6, o16))
-    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 2))
-    terms = [torch.randn(n, width, device=dev) for _ in range(5)]
+    ms = _timed([(lambda t=t: k.add_rms_norm(t[0], t[1], w, 1e-6, t[4])) for t in sets])         # 8 x 32 MB: twice the L2
+    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 4 + 2))
+    del sets
     coef = torch.ones(5, device=dev)
-    ms = _timed(lambda: k.depth_mix(terms, coef, None, False, o32, o16))
+    sets = [[torch.randn(n, width, device=dev) for _ in range(5)] for _ in range(3)]
+    ms = _timed([(lambda t=t: k.depth_mix(t, coef, None, False, o32, o16)) for t in sets])
     mem_row("depth_mix_5_terms", ms, n * width * (5 * 4 + 4 + 2))
+    del sets
 
     # ---- per-head products ---------------------------------------------------------------------------------------------
     for n in (2048, 8):
         qd = torch.randn(n, heads * (dim + rot), device=dev).to(bf)
         uk = torch.randn(heads * dim, rank, device=dev).to(bf) * 0.05
         q_cat = torch.empty(n, heads * lw, device=dev, dtype=bf)
-        uks = [uk.clone() for _ in range(70 if n <= 8 else 1)]
+        uks = [uk.clone() for _ in range(70 if n <= 8 else 1)] * (1 if n <= 8 else 8)        # many rows: flop-bound, operands may wait in the L2
         ms = _timed([(lambda u=u: k.head_linear(qd, 0, dim + rot, u, dim * rank, rank, 1, q_cat, 0, lw, num_heads=heads, n_in=dim, n_out=rank))
                      for u in uks])
         (flop_row if n >= 128 else mem_row)(f"query_into_latent_{n}", ms, 2.0 * n * heads * dim * rank if n >= 128 else heads * dim * rank * 2)
         lat = torch.randn(n, heads * rank, device=dev).to(bf)
         uv = torch.randn(heads * vdim, rank, device=dev).to(bf) * 0.05
         hv = torch.empty(n, heads * vdim, device=dev, dtype=bf)
-        uvs = [uv.clone() for _ in range(70 if n <= 8 else 1)]
+        uvs = [uv.clone() for _ in range(70 if n <= 8 else 1)] * (1 if n <= 8 else 8)
         ms = _timed([(lambda u=u: k.head_linear(lat, 0, rank, u, vdim * rank, 1, rank, hv, 0, vdim, num_heads=heads, n_in=rank, n_out=vdim))
                      for u in uvs])
         (flop_row if n >= 128 else mem_row)(f"values_out_of_latent_{n}", ms, 2.0 * n * heads * vdim * rank if n >= 128 else heads * vdim * rank * 2)

@@ -57,6 +57,119 @@ __global__ void gated_add_layer_norm_kernel(const float * __restrict__ x, const 
     }
 }
 
+// four consecutive elements as float4: 16-byte (float) or 8-byte (bfloat16) accesses
+template <typename T> struct V4;
+template <> struct V4<float> {
+    static __device__ __forceinline__ float4 load(const float * p) { return *reinterpret_cast<const float4 *>(p); }
+    static __device__ __forceinline__ void store(float * p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+};
+template <> struct V4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16 * p) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 * p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned *>(&a);
+        raw.y = *reinterpret_cast<unsigned *>(&b);
+        *reinterpret_cast<uint2 *>(p) = raw;
+    }
+};
+
+// The same for H % 4 == 0, H <= 16 * blockDim and aligned operands: the row stays in registers (thread t owns the
+// groups of four t, t + blockDim, ...: fixed by H alone), one pass over memory, wide accesses.  The sums run over the
+// same values as in the general form; their order differs, so a model uses one form or the other for a given H.
+template <typename A, typename G, int VPT>
+__global__ void gated_add_layer_norm_vec_kernel(const float * __restrict__ x, const A * __restrict__ sub, long long ld_sub,
+                                                const G * __restrict__ glogit, long long ld_g, const float * __restrict__ gbias,
+                                                const float * __restrict__ w, const float * __restrict__ b,
+                                                float * __restrict__ out, A * __restrict__ out_act,
+                                                int H, float alpha, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    const int groups = H >> 2;
+    float4 v[VPT];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int gi = threadIdx.x + k * blockDim.x;
+        if (gi < groups) {
+            float4 t = V4<float>::load(x + n * H + 4 * gi);
+            t.x *= alpha; t.y *= alpha; t.z *= alpha; t.w *= alpha;
+            if (sub != nullptr) {
+                float4 s4 = V4<A>::load(sub + n * ld_sub + 4 * gi);
+                if (glogit != nullptr) {
+                    float4 g4 = V4<G>::load(glogit + n * ld_g + 4 * gi);
+                    if (gbias != nullptr) {
+                        const float4 b4 = V4<float>::load(gbias + 4 * gi);
+                        g4.x += b4.x; g4.y += b4.y; g4.z += b4.z; g4.w += b4.w;
+                    }
+                    s4.x *= sigmoid_f(g4.x); s4.y *= sigmoid_f(g4.y); s4.z *= sigmoid_f(g4.z); s4.w *= sigmoid_f(g4.w);
+                }
+                t.x += s4.x; t.y += s4.y; t.z += s4.z; t.w += s4.w;
+            }
+            v[k] = t;
+            sum += (t.x + t.y) + (t.z + t.w);
+        }
+    }
+    const float mean = block_sum(sum, scratch) / (float) H;
+    float dev = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int gi = threadIdx.x + k * blockDim.x;
+        if (gi < groups) {
+            const float dx = v[k].x - mean, dy = v[k].y - mean, dz = v[k].z - mean, dw = v[k].w - mean;
+            dev += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(dev, scratch) / (float) H + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int gi = threadIdx.x + k * blockDim.x;
+        if (gi < groups) {
+            const float4 w4 = V4<float>::load(w + 4 * gi);
+            float4 y = make_float4((v[k].x - mean) * inv * w4.x, (v[k].y - mean) * inv * w4.y, (v[k].z - mean) * inv * w4.z,
+                                   (v[k].w - mean) * inv * w4.w);
+            if (b != nullptr) {
+                const float4 b4 = V4<float>::load(b + 4 * gi);
+                y.x += b4.x; y.y += b4.y; y.z += b4.z; y.w += b4.w;
+            }
+            if (out != nullptr) V4<float>::store(out + n * H + 4 * gi, y);
+            if (out_act != nullptr) V4<A>::store(out_act + n * H + 4 * gi, y);
+        }
+    }
+}
+
+// depth mix, four columns a thread (H % 4 == 0, aligned streams)
+template <typename A>
+__global__ void depth_mix_vec_kernel(MixTerms terms, int n_terms, const float * __restrict__ coef, const int * __restrict__ rows,
+                                     int n_src, int last_is_selected, float * __restrict__ out, A * __restrict__ out_act, int H) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t r = blockIdx.x;
+    long long src = (long long) r;
+    if (rows != nullptr) src = rows[r];
+    const bool src_ok = src >= 0 && src < n_src;
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < n_terms; j++) {
+            const bool own = rows == nullptr || (last_is_selected && j == n_terms - 1);
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (own) v = V4<float>::load(terms.x[j] + r * H + i);
+            else if (src_ok) v = V4<float>::load(terms.x[j] + (size_t) src * H + i);
+            const float c = coef[j];
+            acc.x = fmaf(c, v.x, acc.x); acc.y = fmaf(c, v.y, acc.y); acc.z = fmaf(c, v.z, acc.z); acc.w = fmaf(c, v.w, acc.w);
+        }
+        if (out != nullptr) V4<float>::store(out + r * H + i, acc);
+        if (out_act != nullptr) V4<A>::store(out_act + r * H + i, acc);
+    }
+}
+
 template <typename A>
 __global__ void depth_mix_kernel(MixTerms terms, int n_terms, const float * __restrict__ coef, const int * __restrict__ rows,
                                  int n_src, int last_is_selected, float * __restrict__ out, A * __restrict__ out_act, int H) {
@@ -116,10 +229,25 @@ IIAN_API int iian_gated_add_layer_norm(const float * x, const void * sub, long l
     if (N <= 0) return IIAN_OK;
     if (H <= 0 || (size_t) H * 4 > 200 * 1024) return IIAN_ERR_LIMIT;
     const size_t smem = (size_t) H * 4;
-    const int threads = norm_threads(H);
+    int threads = norm_threads(H);
     typedef __nv_bfloat16 bf;
+    // the register form: a function of H and of the operands' alignment alone, never of the batch
+    const size_t a_al = act_dtype == IIAN_BF16 ? 7 : 15, g_al = gate_dtype == IIAN_BF16 ? 7 : 15;
+    const size_t a_ld = 4, g_ld = 4;
+    const bool vec = H % 4 == 0 && H <= 16 * 1024 && ((uintptr_t) x & 15) == 0 && ((uintptr_t) w & 15) == 0 && ((uintptr_t) b & 15) == 0 &&
+                     ((uintptr_t) gbias & 15) == 0 && ((uintptr_t) out & 15) == 0 && ((uintptr_t) out_act & a_al) == 0 &&
+                     ((uintptr_t) sub & a_al) == 0 && ld_sub % (long long) a_ld == 0 && ((uintptr_t) glogit & g_al) == 0 &&
+                     ld_g % (long long) g_ld == 0;
+    if (vec) {
+        const int groups = H / 4;
+        threads = 128;
+        while (threads < 1024 && threads * 4 < groups) threads *= 2;
+    }
 #define IIAN_GLN(AT, GT)                                                                                                     \
     do {                                                                                                                     \
+        if (vec)                                                                                                             \
+            return iian_launch(gated_add_layer_norm_vec_kernel<AT, GT, 4>, dim3(N), dim3(threads), 0, stream, x, (const AT *) sub, \
+                               ld_sub, (const GT *) glogit, ld_g, gbias, w, b, out, (AT *) out_act, H, alpha, eps);          \
         if (smem > 48 * 1024) cudaFuncSetAttribute(gated_add_layer_norm_kernel<AT, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
         return iian_launch(gated_add_layer_norm_kernel<AT, GT>, dim3(N), dim3(threads), smem, stream, x, (const AT *) sub, ld_sub, \
                            (const GT *) glogit, ld_g, gbias, w, b, out, (AT *) out_act, H, alpha, eps);                      \
@@ -140,6 +268,14 @@ IIAN_API int iian_depth_mix(const float * const * terms, int n_terms, const floa
     MixTerms t;
     for (int j = 0; j < kMaxMixTerms; j++) t.x[j] = j < n_terms ? terms[j] : nullptr;
     const int threads = norm_threads(H);
+    bool vec = H % 4 == 0 && ((uintptr_t) out & 15) == 0 && ((uintptr_t) out_act & (act_dtype == IIAN_BF16 ? 7 : 15)) == 0;
+    for (int j = 0; j < n_terms; j++) vec = vec && ((uintptr_t) terms[j] & 15) == 0;
+    if (vec) {
+        const int vt = H >= 2048 ? 256 : 128;
+        if (act_dtype == IIAN_F32) return iian_launch(depth_mix_vec_kernel<float>, dim3(R), dim3(vt), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (float *) out_act, H);
+        if (act_dtype == IIAN_BF16) return iian_launch(depth_mix_vec_kernel<__nv_bfloat16>, dim3(R), dim3(vt), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (__nv_bfloat16 *) out_act, H);
+        return IIAN_ERR_DTYPE;
+    }
     if (act_dtype == IIAN_F32) return iian_launch(depth_mix_kernel<float>, dim3(R), dim3(threads), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (float *) out_act, H);
     if (act_dtype == IIAN_BF16) return iian_launch(depth_mix_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, t, n_terms, coef, rows, n_src, last_is_selected, out, (__nv_bfloat16 *) out_act, H);
     return IIAN_ERR_DTYPE;
