@@ -213,7 +213,7 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     ms = _timed([(lambda t=t: k.gated_add_layer_norm(t[0], t[1], t[2], gb, w, b, 2.0, 1e-6, t[3], t[4])) for t in sets])
     mem_row("gated_sum_layer_norm", ms, n * width * (4 + 2 + 2 + 4 + 2))
     ms = _timed([(lambda t=t: k.add_rms_norm(t[0], t[1], w, 1e-6, t[4])) for t in sets])         # 8 x 32 MB: twice the L2
-    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 4 + 2))
+    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 2))
     del sets
     coef = torch.ones(5, device=dev)
     sets = [[torch.randn(n, width, device=dev) for _ in range(5)] for _ in range(3)]
