@@ -38,10 +38,10 @@ def layer(mix, mlp):
 #    three, a window that is no multiple of the page size.   R: one head, one expert of one, no rotation in one layer.
 CONFIGS = {
     "P": {"architecture": "Galodra", "vocab": 211, "width": 96, "norm": {"eps": 1e-5}, "postln_alpha": 1.7, "layers": [
-        layer(mixer(3, 16, 12, 24, 40, 24, 8, 50000.0), dense(160)),
+        layer(mixer(3, 16, 12, 24, 40, 24, 8, 30000.0), dense(160)),
         layer(mixer(3, 16, 12, 24, 40, None, 12), moe(5, 2, 48)),
         layer(mixer(2, 24, 8, 16, 24, 17, 8), None),
-        layer(mixer(3, 16, 12, 24, 40, 24, 8, 50000.0), moe(5, 2, 48))]},
+        layer(mixer(3, 16, 12, 24, 40, 24, 8, 30000.0), moe(5, 2, 48))]},
     "Q": {"architecture": "Galodra", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "postln_alpha": 3.0, "layers": [
         layer(mixer(4, 32, 32, 32, 64, 33, 32), moe(8, 1, 64)),
         layer(mixer(4, 32, 32, 32, 64, 33, 32), dense(256)),
