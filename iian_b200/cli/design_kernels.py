@@ -9,7 +9,7 @@ flops are the algorithmic ones (what the operation has to read and write, or mul
 bandwidth and bfloat16 product peak.
 
 Pairs (width 2048, 16 heads; latent rank 512 + 64 rotated; Qwen3 side: 16 heads of 128 on 8 KV heads):
-  decode attention   8 sequences of 4,096 cached tokens, one new token each       bytes of cache read
+  decode attention   8 (and 64) sequences of 4,096 cached tokens, one new token each   bytes of cache read
   prefill attention  one sequence of 2,048 tokens                                 flops of scores and values
   expert products    2,048 tokens x 6 of 64 experts (1,408 wide)  vs  the dense gate/up and down products of 8,448
   sum + norm         2,048 rows: gated sum with LayerNorm  vs  residual add with RMSNorm
@@ -97,28 +97,30 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     def flop_row(name, ms, flops):
         out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "of_bf16_peak": flops / ms / 1e9 / tfl}
 
-    # ---- decode attention --------------------------------------------------------------------------------------------
-    B, ctx = 8, 4096
-    meta, pages = _meta([ctx] * B, [1] * B, page, dev)
-    rows = torch.randn(pages, page, lw, device=dev).to(bf) * 0.3
-    q = torch.randn(B, heads, lw, device=dev).to(bf) * 0.1
-    o = torch.empty(B, heads, rank, device=dev, dtype=bf)
+    # ---- decode attention: a short step (bound by its fixed costs: two launches, the first tile, the merge) and a long one ----
     sink = torch.zeros(heads, device=dev)
-    copies = [rows.clone() for _ in range(5)]
-    ms = _timed([(lambda r=r: k.latent_attention_mma(q, r, o, sink, meta, num_heads=heads, rank=rank, scale=0.07, window=window))
-                 for r in copies])
-    mem_row("decode_attention_latent", ms, B * ctx * lw * 2)
-    del copies
     nkv, hd = 8, 128
-    kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
-    vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
-    q2 = torch.randn(B, heads, hd, device=dev).to(bf) * 0.1
-    o2 = torch.empty(B, heads * hd, device=dev, dtype=bf)
-    copies = [(kc.clone(), vc.clone()) for _ in range(3)]
-    ms = _timed([(lambda c=c: k.paged_attention(q2, c[0], c[1], o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
-                                                window=window)) for c in copies])
-    mem_row("decode_attention_qwen3", ms, B * ctx * 2 * nkv * hd * 2)
-    del copies
+    for B, ctx in ((8, 4096), (64, 4096)):
+        tag = "" if B == 8 else f"_{B}x{ctx}"
+        meta, pages = _meta([ctx] * B, [1] * B, page, dev)
+        n_copies = 5 if B == 8 else 2
+        copies = [torch.randn(pages, page, lw, device=dev).to(bf) * 0.3 for _ in range(n_copies)]
+        q = torch.randn(B, heads, lw, device=dev).to(bf) * 0.1
+        o = torch.empty(B, heads, rank, device=dev, dtype=bf)
+        ms = _timed([(lambda r=r: k.latent_attention_mma(q, r, o, sink, meta, num_heads=heads, rank=rank, scale=0.07, window=window))
+                     for r in copies])
+        mem_row("decode_attention_latent" + tag, ms, B * ctx * lw * 2)
+        del copies
+        n_copies = 3 if B == 8 else 2
+        copies = [(torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3, torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3)
+                  for _ in range(n_copies)]
+        q2 = torch.randn(B, heads, hd, device=dev).to(bf) * 0.1
+        o2 = torch.empty(B, heads * hd, device=dev, dtype=bf)
+        ms = _timed([(lambda c=c: k.paged_attention(q2, c[0], c[1], o2, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                    window=window)) for c in copies])
+        mem_row("decode_attention_qwen3" + tag, ms, B * ctx * 2 * nkv * hd * 2)
+        del copies
+    torch.cuda.empty_cache()
 
     # ---- prefill attention -------------------------------------------------------------------------------------------
     T = 2048
