@@ -240,8 +240,8 @@ IIAN_API int iian_gated_add_layer_norm(const float * x, const void * sub, long l
                      ld_g % (long long) g_ld == 0;
     if (vec) {
         const int groups = H / 4;
-        threads = 128;
-        while (threads < 1024 && threads * 4 < groups) threads *= 2;
+        threads = 128;                                       // a group of four a thread up to 1024 threads, then up to four
+        while (threads < 1024 && threads < groups) threads *= 2;
     }
 #define IIAN_GLN(AT, GT)                                                                                                     \
     do {                                                                                                                     \
