@@ -61,11 +61,14 @@ class LayerCall:
     ``layer`` indexes ``ModelSpec.layers`` (a layer may be called more than once);
     ``cache`` is the cache this call's mixer works on.  A call that does not own its cache
     (``writes_cache=False``) reads what an earlier call with the same ``cache`` id stored.
+    ``before`` names an entry of ``ModelSpec.stream_parts`` that transforms the stream right
+    before this call's layer runs (None: nothing).
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
+    before: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -78,10 +81,15 @@ class ModelSpec:
     order: Sequence[LayerCall]
     final_norm: PartSpec
     head: PartSpec
+    # parts that work on the whole stream between layers (``LayerCall.before`` names one by its index here)
+    stream_parts: Sequence[PartSpec] = ()
 
     def validate(self) -> None:
         owners: dict[int, int] = {}
         for idx, call in enumerate(self.order):
+            if call.before is not None and not 0 <= call.before < len(self.stream_parts):
+                raise ValueError(f"run order entry {idx} names stream part {call.before}, "
+                                 f"but the model has {len(self.stream_parts)}")
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"run order entry {idx} names layer {call.layer}, "
                                  f"but the model has {len(self.layers)} layers")

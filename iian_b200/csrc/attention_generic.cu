@@ -8,6 +8,10 @@
 // Formula (reference): head h reads KV head h / (nh / nkv); s_j = (q . k_j) * scale; key j is
 // visible iff j <= pos and (window == 0 or pos - j < window); softmax in float32; o = sum p_j v_j
 // (src/iian/paged_attn.cpp:112-145, window test :124).
+//
+// Two options beyond the reference's formula, for mixers that have them: a sink per head (a logit with no key and no
+// value that joins the softmax's denominator once, unscaled: the running softmax simply starts at maximum sink_h with
+// denominator 1), and an output gate (o *= sigmoid(g) element by element, g read from rows of a wider matrix).
 #include "common.cuh"
 
 namespace iian {
@@ -20,7 +24,8 @@ __global__ void paged_attention_generic_kernel(
     const A * __restrict__ q, const A * __restrict__ k_cache, const A * __restrict__ v_cache,
     A * __restrict__ out, const int * __restrict__ positions, const int * __restrict__ seq_of_token,
     const int * __restrict__ block_table, int max_blocks, const int * __restrict__ ctx_len,
-    int N, int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window) {
+    int N, int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+    const float * __restrict__ sink, const A * __restrict__ gate, long long ld_gate) {
     __shared__ float qs[kGenWarps][kGenMaxHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long) blockIdx.x * kGenWarps + warp;
@@ -46,7 +51,7 @@ __global__ void paged_attention_generic_kernel(
     float acc[kAcc];
 #pragma unroll
     for (int i = 0; i < kAcc; i++) acc[i] = 0.0f;
-    float m = -INFINITY, l = 0.0f;
+    float m = sink != nullptr ? sink[h] : -INFINITY, l = sink != nullptr ? 1.0f : 0.0f;
     const int * bt = block_table + (size_t) s * max_blocks;
 
     for (int kb = (lo / 32) * 32; kb <= hi; kb += 32) {
@@ -95,7 +100,11 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
     for (int i = 0; i < kAcc; i++) {
         const int d = lane + 32 * i;
-        if (d < hd) o[d] = from_f32<A>(acc[i] * inv);
+        if (d < hd) {
+            float v = acc[i] * inv;
+            if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t) t * ld_gate + h * hd + d])));
+            o[d] = from_f32<A>(v);
+        }
     }
 }
 
@@ -105,11 +114,12 @@ using namespace iian;
 
 // q: [N, nh, hd]; caches: [num_pages, nkv, page_size, hd]; out: [N, nh * hd];
 // block_table: [S, max_blocks]; ctx_len may be null (then only causality bounds the keys).
-IIAN_API int iian_paged_attention_generic(
+// sink: f32 [nh] or null; gate: rows of nh * hd with row stride ld_gate, or null
+IIAN_API int iian_paged_attention_sink(
     const void * q, const void * k_cache, const void * v_cache, void * out,
     const int * positions, const int * seq_of_token, const int * block_table, int max_blocks,
     const int * ctx_len, int act_dtype, int N, int nh, int nkv, int hd, int page_size, int num_pages,
-    float scale, int window, cudaStream_t stream) {
+    float scale, int window, const float * sink, const void * gate, long long ld_gate, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     if (hd <= 0 || hd > kGenMaxHeadDim || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return IIAN_ERR_SHAPE;
     const long long items = (long long) N * nh;
@@ -118,12 +128,22 @@ IIAN_API int iian_paged_attention_generic(
     if (act_dtype == IIAN_F32)
         paged_attention_generic_kernel<float><<<blocks, threads, 0, stream>>>(
             (const float *) q, (const float *) k_cache, (const float *) v_cache, (float *) out, positions,
-            seq_of_token, block_table, max_blocks, ctx_len, N, nh, nkv, hd, page_size, num_pages, scale, window);
+            seq_of_token, block_table, max_blocks, ctx_len, N, nh, nkv, hd, page_size, num_pages, scale, window, sink,
+            (const float *) gate, ld_gate);
     else if (act_dtype == IIAN_BF16)
         paged_attention_generic_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
             (const __nv_bfloat16 *) q, (const __nv_bfloat16 *) k_cache, (const __nv_bfloat16 *) v_cache,
             (__nv_bfloat16 *) out, positions, seq_of_token, block_table, max_blocks, ctx_len, N, nh, nkv, hd,
-            page_size, num_pages, scale, window);
+            page_size, num_pages, scale, window, sink, (const __nv_bfloat16 *) gate, ld_gate);
     else return IIAN_ERR_DTYPE;
     return iian_launch_status();
+}
+
+IIAN_API int iian_paged_attention_generic(
+    const void * q, const void * k_cache, const void * v_cache, void * out,
+    const int * positions, const int * seq_of_token, const int * block_table, int max_blocks,
+    const int * ctx_len, int act_dtype, int N, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, cudaStream_t stream) {
+    return iian_paged_attention_sink(q, k_cache, v_cache, out, positions, seq_of_token, block_table, max_blocks, ctx_len, act_dtype,
+                                     N, nh, nkv, hd, page_size, num_pages, scale, window, nullptr, nullptr, 0, stream);
 }

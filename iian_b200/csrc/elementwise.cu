@@ -14,7 +14,7 @@ namespace iian {
 
 template <typename W>
 __global__ void embedding_kernel(const W * __restrict__ table, const int * __restrict__ tokens,
-                                 float * __restrict__ out, int H, int V) {
+                                 float * __restrict__ out, int H, int V, float scale) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -25,13 +25,14 @@ __global__ void embedding_kernel(const W * __restrict__ table, const int * __res
         return;
     }
     const W * row = table + (size_t) id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;     // scale 1: the row itself
 }
 
-// residual (f32, in place) += delta (A, optional); out (A) = rmsnorm(residual) * weight (f32)
+// residual (f32, in place) += delta (A, optional) [+ delta2 (A, optional, only with delta): r + (d + d2)];
+// out (A) = rmsnorm(residual) * weight (f32)
 // General form: two passes over the row, any H.
 template <typename A>
-__global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta,
+__global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta, const A * __restrict__ delta2,
                                     const float * __restrict__ weight, A * __restrict__ out,
                                     int H, float eps) {
     pdl_wait();
@@ -42,8 +43,9 @@ __global__ void add_rms_norm_kernel(float * __restrict__ residual, const A * __r
     float ss = 0.0f;
     if (delta != nullptr) {
         const A * d = delta + base;
+        const A * d2 = delta2 != nullptr ? delta2 + base : nullptr;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = r[i] + to_f32(d[i]);
+            const float v = r[i] + (d2 != nullptr ? to_f32(d[i]) + to_f32(d2[i]) : to_f32(d[i]));
             r[i] = v;
             ss += v * v;
         }
@@ -83,7 +85,7 @@ template <> struct Vec4<__nv_bfloat16> {
 // Fast form for H % 4 == 0 and H <= 4 * VPT * blockDim: the row stays in registers, one pass over
 // memory, 16-byte accesses.  Thread t owns the float4 groups t, t + blockDim, ... (fixed by H alone).
 template <typename A, int VPT>
-__global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta,
+__global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta, const A * __restrict__ delta2,
                                         const float * __restrict__ weight, A * __restrict__ out,
                                         int H, float eps) {
     pdl_wait();
@@ -99,7 +101,11 @@ __global__ void add_rms_norm_vec_kernel(float * __restrict__ residual, const A *
         if (gi < groups) {
             float4 x = Vec4<float>::load(residual + base + 4 * gi);
             if (delta != nullptr) {
-                const float4 d = Vec4<A>::load(delta + base + 4 * gi);
+                float4 d = Vec4<A>::load(delta + base + 4 * gi);
+                if (delta2 != nullptr) {
+                    const float4 e = Vec4<A>::load(delta2 + base + 4 * gi);
+                    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+                }
                 x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
                 Vec4<float>::store(residual + base + 4 * gi, x);
             }
@@ -206,34 +212,51 @@ __global__ void add_bias_kernel(A * __restrict__ x, const float * __restrict__ b
 
 using namespace iian;
 
-IIAN_API int iian_embedding(const void * table, int table_dtype, const int * tokens, float * out,
-                            int N, int H, int V, cudaStream_t stream) {
+// out[t, :] = table[tokens[t], :] * scale, in float32
+IIAN_API int iian_embedding_scaled(const void * table, int table_dtype, const int * tokens, float * out,
+                                   int N, int H, int V, float scale, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     const int threads = H >= 1024 ? 256 : 128;
-    if (table_dtype == IIAN_F32) return iian_launch(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) table, tokens, out, H, V);
-    if (table_dtype == IIAN_BF16) return iian_launch(embedding_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) table, tokens, out, H, V);
+    if (table_dtype == IIAN_F32) return iian_launch(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) table, tokens, out, H, V, scale);
+    if (table_dtype == IIAN_BF16) return iian_launch(embedding_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) table, tokens, out, H, V, scale);
     return IIAN_ERR_DTYPE;
 }
 
+IIAN_API int iian_embedding(const void * table, int table_dtype, const int * tokens, float * out,
+                            int N, int H, int V, cudaStream_t stream) {
+    return iian_embedding_scaled(table, table_dtype, tokens, out, N, H, V, 1.0f, stream);
+}
+
+IIAN_API int iian_add2_rms_norm(float * residual, const void * delta, const void * delta2, const float * weight, void * out,
+                                int act_dtype, int N, int H, float eps, cudaStream_t stream);
+
 IIAN_API int iian_add_rms_norm(float * residual, const void * delta, const float * weight, void * out,
                                int act_dtype, int N, int H, float eps, cudaStream_t stream) {
+    return iian_add2_rms_norm(residual, delta, nullptr, weight, out, act_dtype, N, H, eps, stream);
+}
+
+// residual += delta + delta2 (the two summed first; delta2 only with delta), then the norm
+IIAN_API int iian_add2_rms_norm(float * residual, const void * delta, const void * delta2, const float * weight, void * out,
+                                int act_dtype, int N, int H, float eps, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
+    if (delta == nullptr && delta2 != nullptr) return IIAN_ERR_SHAPE;
     if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
     // the launch shape is a function of H alone, so the order of every sum does not depend on the batch
     const bool aligned = H % 4 == 0 && ((uintptr_t) residual & 15) == 0 && ((uintptr_t) weight & 15) == 0 &&
-                         ((uintptr_t) out & 7) == 0 && ((uintptr_t) delta & 7) == 0;
+                         ((uintptr_t) out & 7) == 0 && ((uintptr_t) delta & 7) == 0 &&
+                         ((uintptr_t) delta2 & 7) == 0;
     if (aligned && H <= 4 * 4 * 1024) {
         const int groups = H / 4;
         int threads = 128;
         while (threads < 1024 && threads * 2 <= groups) threads *= 2;      // >= 2 groups per thread up to 1024 threads
         while (threads * 4 < groups) threads *= 2;
         if (threads > 1024) threads = 1024;
-        if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_vec_kernel<float, 4>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, weight, (float *) out, H, eps);
-        return iian_launch(add_rms_norm_vec_kernel<__nv_bfloat16, 4>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
+        if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_vec_kernel<float, 4>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, (const float *) delta2, weight, (float *) out, H, eps);
+        return iian_launch(add_rms_norm_vec_kernel<__nv_bfloat16, 4>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, (const __nv_bfloat16 *) delta2, weight, (__nv_bfloat16 *) out, H, eps);
     }
     const int threads = 256;
-    if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, weight, (float *) out, H, eps);
-    return iian_launch(add_rms_norm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, weight, (__nv_bfloat16 *) out, H, eps);
+    if (act_dtype == IIAN_F32) return iian_launch(add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta, (const float *) delta2, weight, (float *) out, H, eps);
+    return iian_launch(add_rms_norm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual, (const __nv_bfloat16 *) delta, (const __nv_bfloat16 *) delta2, weight, (__nv_bfloat16 *) out, H, eps);
 }
 
 IIAN_API int iian_rms_norm(const void * x, const float * weight, void * out, int act_dtype, int N, int H,

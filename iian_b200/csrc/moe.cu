@@ -48,6 +48,23 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, long long ld
     }
 }
 
+// Routing without a router: row `tokens[t]` of a table [V, top] names the token's experts (the entries of a row differ);
+// each weighs `weight`.  rows (optional): the token of output row r is tokens[rows[r]].
+__global__ void moe_table_route_kernel(const int * __restrict__ tokens, const int * __restrict__ rows, const int * __restrict__ table,
+                                       int V, int E, int top, int * __restrict__ ids, float * __restrict__ wts, float weight, int N,
+                                       int n_tokens) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long) N * top) return;
+    const int r = (int) (i / top), k = (int) (i - (long long) r * top);
+    int t = rows != nullptr ? rows[r] : r;
+    t = min(max(t, 0), n_tokens - 1);
+    const int tok = min(max(tokens[t], 0), V - 1);          // never read outside the table
+    ids[i] = min(max(table[(size_t) tok * top + k], 0), E - 1);
+    wts[i] = weight;
+}
+
 // One block.  offsets: [E + 1] first sorted row of each expert; pos: [M] sorted row of each (token, choice);
 // tiles: [2 * max_tiles + 1]: n_tiles, then (expert, first row) per row tile of tile_rows rows.
 __global__ void moe_plan_kernel(const int * __restrict__ ids, int M, int E, int * __restrict__ offsets, int * __restrict__ pos,
@@ -89,29 +106,40 @@ __global__ void moe_scatter_kernel(const A * __restrict__ h, const int * __restr
     pdl_launch_dependents();
     const size_t i = blockIdx.x;              // (token, choice)
     const size_t t = i / top;
-    const float w = wts[i];
+    const float w = wts != nullptr ? wts[i] : 1.0f;
     const A * src = h + t * W;
     A * dst = xs + (size_t) pos[i] * W;
     for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = from_f32<A>(w * to_f32(src[c]));
 }
 
-// out[t, :] = sum_k ys[pos[t * top + k], :]  (k ascending)
+// out[t, :] = sum_k [wts[t, k] *] ys[pos[t * top + k], :]  (k ascending)
 template <typename A>
-__global__ void moe_combine_kernel(const A * __restrict__ ys, const int * __restrict__ pos, A * __restrict__ out, int W, int top) {
+__global__ void moe_combine_kernel(const A * __restrict__ ys, const int * __restrict__ pos, const float * __restrict__ wts,
+                                   A * __restrict__ out, int W, int top) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = 0.0f;
-        for (int k = 0; k < top; k++) acc += to_f32(ys[(size_t) pos[t * top + k] * W + c]);
+        for (int k = 0; k < top; k++) {
+            const float y = to_f32(ys[(size_t) pos[t * top + k] * W + c]);
+            acc += wts != nullptr ? wts[t * top + k] * y : y;
+        }
         out[t * W + c] = from_f32<A>(acc);
     }
 }
 
-__device__ __forceinline__ float moe_act(float z, int act) {
-    if (act == 0) return z / (1.0f + expf(-z));
-    const float t = 0.7978845608028654f * (z + 0.044715f * z * z * z);
-    return 0.5f * z * (1.0f + tanhf(t));
+// act 0: silu(g) * u; 1: gelu_tanh(g) * u; 2: with g' = min(g, limit), u' = clamp(u, -limit, limit):
+// g' sigmoid(1.702 g') (u' + 1)
+__device__ __forceinline__ float moe_gated(float g, float u, int act, float limit) {
+    if (act == 0) return g / (1.0f + expf(-g)) * u;
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    const float t = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(t)) * u;
 }
 
 // Rows [r0, r0 + rows) of x (sorted by expert) times expert e's weight block w[e] ([n_out, K], row-major):
@@ -122,7 +150,7 @@ template <typename A, typename WT, bool GATED>
 __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restrict__ x, const WT * __restrict__ w,
                                                                const WT * __restrict__ w2, A * __restrict__ out,
                                                                const int * __restrict__ offsets, const int * __restrict__ tiles,
-                                                               int n_out, int K, int act) {
+                                                               int n_out, int K, int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     if ((int) blockIdx.y >= tiles[0]) return;
@@ -187,7 +215,7 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A * __restr
             if (m >= n_out) continue;
             float v = acc[i][j];
             // the gate and up products are rounded to the activation type first, as separate products would leave them
-            if (GATED) v = moe_act(to_f32(from_f32<A>(v)), act) * to_f32(from_f32<A>(acc2[i][j]));
+            if (GATED) v = moe_gated(to_f32(from_f32<A>(v)), to_f32(from_f32<A>(acc2[i][j])), act, limit);
             out[(size_t) r * n_out + m] = from_f32<A>(v);
         }
     }
@@ -205,6 +233,16 @@ IIAN_API int iian_moe_route(const float * logits, long long ld, int E, int top, 
     if (E <= 0 || top <= 0 || top > E || E > 2048) return IIAN_ERR_SHAPE;
     const int warps = 4;
     return iian_launch(moe_route_kernel, dim3((N + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, ld, E, top, ids, wts, N);
+}
+
+// tokens i32 [n_tokens], rows i32 [N] or null (then N == n_tokens), table i32 [V, top] -> ids i32 [N, top], wts f32 [N, top]
+IIAN_API int iian_moe_table_route(const int * tokens, const int * rows, const int * table, int V, int E, int top, int * ids,
+                                  float * wts, float weight, int N, int n_tokens, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (E <= 0 || top <= 0 || top > E || E > 2048 || V <= 0 || n_tokens <= 0) return IIAN_ERR_SHAPE;
+    const long long total = (long long) N * top;
+    return iian_launch(moe_table_route_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, stream, tokens, rows, table, V, E,
+                       top, ids, wts, weight, N, n_tokens);
 }
 
 // ids [M] -> offsets [E + 1], pos [M], tiles [1 + 2 * max_tiles]
@@ -226,19 +264,26 @@ IIAN_API int iian_moe_scatter(const void * h, const int * pos, const float * wts
     return IIAN_ERR_DTYPE;
 }
 
-IIAN_API int iian_moe_combine(const void * ys, const int * pos, void * out, int act_dtype, int N, int W, int top, cudaStream_t stream) {
+// wts: f32 [N, top], the weight of each expert's OUTPUT in the sum, or null (plain sum)
+IIAN_API int iian_moe_combine_weighted(const void * ys, const int * pos, const float * wts, void * out, int act_dtype, int N, int W,
+                                       int top, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     const int threads = W >= 1024 ? 256 : 128;
-    if (act_dtype == IIAN_F32) return iian_launch(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) ys, pos, (float *) out, W, top);
-    if (act_dtype == IIAN_BF16) return iian_launch(moe_combine_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) ys, pos, (__nv_bfloat16 *) out, W, top);
+    if (act_dtype == IIAN_F32) return iian_launch(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) ys, pos, wts, (float *) out, W, top);
+    if (act_dtype == IIAN_BF16) return iian_launch(moe_combine_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) ys, pos, wts, (__nv_bfloat16 *) out, W, top);
     return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_moe_combine(const void * ys, const int * pos, void * out, int act_dtype, int N, int W, int top, cudaStream_t stream) {
+    return iian_moe_combine_weighted(ys, pos, nullptr, out, act_dtype, N, W, top, stream);
 }
 
 // x [M, K] sorted by expert; w (and w2, for the gated form) [E, n_out, K]; out [M, n_out]; act: 0 silu, 1 gelu (tanh).
 // w2 == w: the gated form over blocks [E, 2 n_out, K] that hold both matrices interleaved in groups of 8 rows.
-// The plan's row tiles must be of iian_moe_tile_rows() rows.
-IIAN_API int iian_moe_grouped_gemm(const void * x, const void * w, const void * w2, void * out, const int * offsets, const int * tiles,
-                                   int max_tiles, int act_dtype, int w_dtype, int n_out, int K, int act, cudaStream_t stream) {
+// The plan's row tiles must be of iian_moe_tile_rows() rows.  act 2 (clamped, see moe_gated) takes `limit`.
+IIAN_API int iian_moe_grouped_gemm_act(const void * x, const void * w, const void * w2, void * out, const int * offsets,
+                                       const int * tiles, int max_tiles, int act_dtype, int w_dtype, int n_out, int K, int act,
+                                       float limit, cudaStream_t stream) {
     if (max_tiles <= 0 || n_out <= 0) return IIAN_OK;
     if (K <= 0 || max_tiles > 65535) return IIAN_ERR_SHAPE;
     dim3 grid((n_out + kTileN - 1) / kTileN, max_tiles);
@@ -247,12 +292,17 @@ IIAN_API int iian_moe_grouped_gemm(const void * x, const void * w, const void * 
     do {                                                                                                                     \
         if (w2 != nullptr)                                                                                                   \
             return iian_launch(moe_grouped_gemm_kernel<AT, WT, true>, grid, dim3(256), 0, stream, (const AT *) x, (const WT *) w, \
-                               (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act);                                  \
+                               (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act, limit);                           \
         return iian_launch(moe_grouped_gemm_kernel<AT, WT, false>, grid, dim3(256), 0, stream, (const AT *) x, (const WT *) w, \
-                           (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act);                                      \
+                           (const WT *) w2, (AT *) out, offsets, tiles, n_out, K, act, limit);                               \
     } while (0)
     if (act_dtype == IIAN_F32 && w_dtype == IIAN_F32) IIAN_MOE(float, float);
     if (act_dtype == IIAN_BF16 && w_dtype == IIAN_BF16) IIAN_MOE(bf, bf);
 #undef IIAN_MOE
     return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_moe_grouped_gemm(const void * x, const void * w, const void * w2, void * out, const int * offsets, const int * tiles,
+                                   int max_tiles, int act_dtype, int w_dtype, int n_out, int K, int act, cudaStream_t stream) {
+    return iian_moe_grouped_gemm_act(x, w, w2, out, offsets, tiles, max_tiles, act_dtype, w_dtype, n_out, K, act, 0.0f, stream);
 }

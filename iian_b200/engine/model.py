@@ -16,7 +16,7 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..config.registry import Architecture, load_model_config
 from ..config.spec import ModelSpec
-from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, STREAM_PARTS
 from ..weights.loader import FileWeights, TensorSpec, WeightSource, load_declared
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -39,6 +39,8 @@ def _scoped_parts(model_parts) -> List[Tuple[tuple, object]]:
     for i, blk in enumerate(model_parts["blocks"]):
         for slot, part in blk.parts():
             out.append((("layer", i, slot), part))
+    for i, part in enumerate(model_parts["stream_parts"]):
+        out.append((("stream", i), part))
     out.append((("final_norm",), model_parts["final_norm"]))
     out.append((("head",), model_parts["head"]))
     return out
@@ -55,6 +57,7 @@ def _build_parts(spec: ModelSpec, dtype: torch.dtype, device: torch.device):
     return {
         "embedding": EMBEDDINGS.build(spec.embedding, dtype, device),
         "blocks": blocks,
+        "stream_parts": [STREAM_PARTS.build(ps, dtype, device) for ps in spec.stream_parts],
         "final_norm": NORMS.build(spec.final_norm, dtype, device),
         "head": HEADS.build(spec.head, dtype, device),
     }
@@ -85,6 +88,7 @@ class Model:
         mp = _build_parts(self.spec, self.dtype, self.device)
         self.embedding = mp["embedding"]
         self.blocks = mp["blocks"]
+        self.stream_parts = mp["stream_parts"]
         self.final_norm = mp["final_norm"]
         self.head = mp["head"]
         scoped = _scoped_parts(mp)
@@ -148,7 +152,7 @@ class Model:
         return needs
 
     def all_parts(self) -> List[object]:
-        out = [self.embedding, self.final_norm, self.head]
+        out = [self.embedding, self.final_norm, self.head] + list(self.stream_parts)
         for blk in self.blocks:
             out.extend(part for _, part in blk.parts())
         return out
@@ -167,7 +171,7 @@ class Model:
             # matrices, the tensor-core attention kernels wherever a part attends over keys and values per head
             if "gemm_simt" in libs:
                 libs.update(build.BF16_PRODUCT_SOURCES)
-            if "attention_generic" in libs:
+            if "rope_kv" in libs:          # the K/V attention mixer with per-head norms (parts/attention.py)
                 libs.update(build.BF16_ATTENTION_SOURCES)
         return sorted(libs)
 
@@ -187,9 +191,20 @@ class Model:
         residual = self.embedding.forward(ctx.tokens, ctx)
         delta = None
         order = self.spec.order
+        # a stream part that reads what the embedding left needs it untouched; the blocks add into the stream in place, so
+        # a copy is kept unless such a part runs first and moves the stream to a buffer of its own
+        keep = [i for i, c in enumerate(order) if c.before is not None and self.stream_parts[c.before].needs_embedding_out]
+        if keep:
+            x0 = residual
+            if keep[0] > 0:
+                x0 = ctx.buf("embedding_out", residual.shape, residual.dtype)
+                x0.copy_(residual)
+            ctx.step_cache["embedding_out"] = x0
         for idx, call in enumerate(order):
             select = ctx.out_rows if idx == len(order) - 1 else None
             block = self.blocks[call.layer]
+            if call.before is not None:
+                residual, delta = self.stream_parts[call.before].forward(residual, delta, ctx)
             extra = {}
             if idx + 1 < len(order) and getattr(block, "accepts_next_norm", False):
                 # the block after this one: its first norm may ride in this block's last product

@@ -901,7 +901,7 @@ class CudaKernels:
                   terms[0].shape[0], 1 if last_is_selected else 0, _cuda(out, "mix out", torch.float32), _cuda(out_act, "mix out"),
                   _code(out_act, "mix out") if out_act is not None else F32, r, h, _stream()), "depth_mix")
 
-    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
     def gated_act(self, gate_up: torch.Tensor, out: torch.Tensor, interleave: int, activation: str) -> None:
         """``out = act(gate) * up`` for rows ``[gate | up]`` (or interleaved in groups of 8); ``gate_up`` may be a column slice."""
@@ -1121,7 +1121,8 @@ class CudaKernels:
                   _cuda(pos, "pos", torch.int32), _cuda(tiles, "tiles", torch.int32), max_tiles,
                   tile_rows or self.moe_tile_rows(), _stream()), "moe_plan")
 
-    def moe_scatter(self, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, xs: torch.Tensor, top: int) -> None:
+    def moe_scatter(self, h: torch.Tensor, pos: torch.Tensor, weights: Optional[torch.Tensor], xs: torch.Tensor, top: int) -> None:
+        """Rows of ``h`` to their places among the rows sorted by expert, times ``weights`` (None: as they are)."""
         n, w = h.shape
         if xs.shape != (n * top, w) or xs.dtype != h.dtype:
             raise KernelError("moe_scatter: xs must be [N * top, W] in the dtype of h")
@@ -1130,7 +1131,7 @@ class CudaKernels:
                   _cuda(xs, "moe rows"), _code(h, "moe in"), n, w, top, _stream()), "moe_scatter")
 
     def moe_grouped_gemm(self, x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], out: torch.Tensor,
-                         offsets: torch.Tensor, tiles: torch.Tensor, activation: str = "silu") -> None:
+                         offsets: torch.Tensor, tiles: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> None:
         """Rows of ``x`` sorted by expert times that expert's block of ``w`` [E, n_out, K]; with ``w2`` the gated form
         ``act(x . w) * (x . w2)``; with ``w2 is w`` the blocks are [E, 2 n_out, K] and hold both matrices interleaved in
         groups of 8 rows."""
@@ -1138,20 +1139,188 @@ class CudaKernels:
         n_out = w.shape[1] // 2 if w2 is w else w.shape[1]
         if w.shape[2] != k or out.shape != (m, n_out) or (w2 is not None and w2.shape != w.shape) or out.dtype != x.dtype:
             raise KernelError(f"moe_grouped_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
-        fn = _fn("moe", "iian_moe_grouped_gemm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                  c_int, c_int, c_int, c_void_p])
+        fn = _fn("moe", "iian_moe_grouped_gemm_act", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                      c_int, c_int, c_int, c_float, c_void_p])
         _check(fn(_cuda(x, "moe rows"), _cuda(w, "expert weights"), _cuda(w2, "expert weights"), _cuda(out, "moe out"),
                   _cuda(offsets, "offsets", torch.int32), _cuda(tiles, "tiles", torch.int32), (tiles.numel() - 1) // 2,
-                  _code(x, "moe rows"), _code(w, "expert weights"), n_out, k, self.ACTIVATIONS[activation], _stream()),
+                  _code(x, "moe rows"), _code(w, "expert weights"), n_out, k, self.ACTIVATIONS[activation], limit, _stream()),
                "moe_grouped_gemm")
 
-    def moe_combine(self, ys: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    def moe_combine(self, ys: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, top: int,
+                    weights: Optional[torch.Tensor] = None) -> None:
+        """``out[t] = sum_k weights[t, k] * ys[pos[t, k]]`` (``weights`` None: the plain sum), k ascending, in float32."""
         n, w = out.shape
-        if ys.shape != (n * top, w) or ys.dtype != out.dtype:
+        if ys.shape != (n * top, w) or ys.dtype != out.dtype or (weights is not None and weights.numel() != n * top):
             raise KernelError("moe_combine: ys must be [N * top, W] in the dtype of out")
-        fn = _fn("moe", "iian_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-        _check(fn(_cuda(ys, "moe out rows"), _cuda(pos, "pos", torch.int32), _cuda(out, "moe out"), _code(out, "moe out"), n, w, top,
-                  _stream()), "moe_combine")
+        fn = _fn("moe", "iian_moe_combine_weighted", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(ys, "moe out rows"), _cuda(pos, "pos", torch.int32), _cuda(weights, "expert weights", torch.float32),
+                  _cuda(out, "moe out"), _code(out, "moe out"), n, w, top, _stream()), "moe_combine")
+
+    # ---- a scaled embedding, a second sub-layer output in the norm's sum (csrc/elementwise.cu) -----------------------
+    def embedding_scaled(self, table: torch.Tensor, tokens: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+        n, h = out.shape
+        fn = _fn("elementwise", "iian_embedding_scaled", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(table, "embedding table"), _code(table, "embedding table"), _cuda(tokens, "tokens", torch.int32),
+                  _cuda(out, "embedding out", torch.float32), n, h, table.shape[0], scale, _stream()), "embedding_scaled")
+
+    def add2_rms_norm(self, residual: torch.Tensor, delta: torch.Tensor, delta2: torch.Tensor, weight: torch.Tensor, eps: float,
+                      out: torch.Tensor) -> None:
+        """``residual += delta + delta2`` (the two summed first, all in float32), then ``out = rmsnorm(residual) * weight``."""
+        n, h = residual.shape
+        for d in (delta, delta2):
+            if d.shape != residual.shape or d.dtype != out.dtype:
+                raise KernelError("add2_rms_norm: a delta does not match the residual's shape or the output's dtype")
+        if out.shape != residual.shape or weight.numel() != h:
+            raise KernelError("add2_rms_norm: shapes of out / weight do not match the residual")
+        fn = _fn("elementwise", "iian_add2_rms_norm",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(residual, "residual", torch.float32), _cuda(delta, "delta"), _cuda(delta2, "delta"),
+                  _cuda(weight, "norm weight", torch.float32), _cuda(out, "norm out"), _code(out, "norm out"), n, h, eps, _stream()),
+               "add2_rms_norm")
+
+    # ---- gates and the re-injected embedding (csrc/stream_ops.cu) --------------------------------------------------------
+    def stream_concat(self, x: torch.Tensor, d1: Optional[torch.Tensor], d2: Optional[torch.Tensor], e: torch.Tensor,
+                      out: torch.Tensor) -> None:
+        """``out[t] = [x_t + (d1_t + d2_t) ; e_t]`` in the dtype of ``out``; ``x``, ``e`` float32 [N, H], ``out`` [N, 2H]."""
+        n, h = x.shape
+        if e.shape != x.shape or out.shape != (n, 2 * h) or any(d is not None and (d.shape != x.shape or d.dtype != out.dtype) for d in (d1, d2)):
+            raise KernelError("stream_concat: shapes or dtypes do not fit")
+        if d1 is None:
+            d1, d2 = d2, None
+        fn = _fn("stream_ops", "iian_stream_concat", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "stream", torch.float32), _cuda(d1, "delta"), _cuda(d2, "delta"), _cuda(e, "embedding out", torch.float32),
+                  _cuda(out, "concat out"), _code(out, "concat out"), n, h, _stream()), "stream_concat")
+
+    def sigmoid_mul(self, x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+        """``out = x * sigmoid(gate)`` element by element; ``gate`` may be a column slice."""
+        n, m = x.shape
+        if gate.shape != (n, m) or out.shape != (n, m) or gate.dtype != x.dtype or out.dtype != x.dtype:
+            raise KernelError("sigmoid_mul: x, gate and out must share shape and dtype")
+        gp, ld = self._rows(gate, "gate")
+        fn = _fn("stream_ops", "iian_sigmoid_mul", [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(x, "gated x"), gp, ld, _cuda(out, "gated out"), _code(x, "gated x"), n, m, _stream()), "sigmoid_mul")
+
+    def head_norm_gate(self, x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *,
+                       num_heads: int, eps: float) -> None:
+        """``out[t, h] = x[t, h] / sqrt(mean(x[t, h]^2) + eps) * weight[h] * sigmoid(gate[t, h])``: every head by its own root
+        mean square.  ``x`` float32 [N, heads * dv]; ``gate`` (optional, may be a column slice) and ``out`` in one dtype."""
+        n, m = x.shape
+        if m % num_heads or weight.numel() != m or out.shape != (n, m) or (gate is not None and (gate.shape != (n, m) or gate.dtype != out.dtype)):
+            raise KernelError("head_norm_gate: shapes or dtypes do not fit")
+        gp, ld = self._rows(gate, "gate")
+        fn = _fn("stream_ops", "iian_head_norm_gate", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int,
+                                                       c_float, c_void_p])
+        _check(fn(_cuda(x, "heads", torch.float32), _cuda(weight, "head norm weight", torch.float32), gp, ld, _cuda(out, "head norm out"),
+                  _code(out, "head norm out"), n, num_heads, m // num_heads, eps, _stream()), "head_norm_gate")
+
+    # ---- attention whose values are its keys (csrc/shared_kv.cu), sink and output gate (csrc/attention_generic.cu) ----------
+    def projection_norm_rope_store(self, proj: torch.Tensor, q_off: int, k_off: int, q_out: torch.Tensor,
+                                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, num_heads: int,
+                                   num_kv_heads: int, head_dim: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                                   eps: float, inv_freq: Optional[torch.Tensor], rot_dim: int, rope_style: int, positions: torch.Tensor,
+                                   slots: Optional[torch.Tensor]) -> None:
+        """From rows of a stacked product (q at column ``q_off``, k at ``k_off``): RMS norm of q and of k over the whole
+        projection, rotation, q into ``q_out`` [N, heads, head_dim], the rotated k into ``k_cache`` and the k as projected into
+        ``v_cache`` at the tokens' cells (``slots``; without caches nothing is stored)."""
+        n = proj.shape[0]
+        pp, ld = self._rows(proj, "projections")
+        if q_off + num_heads * head_dim > proj.shape[1] or k_off + num_kv_heads * head_dim > proj.shape[1] \
+                or q_out.numel() != n * num_heads * head_dim or q_out.dtype != proj.dtype:
+            raise KernelError("projection_norm_rope_store: the projections do not hold these heads")
+        page_size, num_pages = 1, 0
+        if k_cache is not None:
+            if v_cache is None or slots is None or k_cache.dtype != proj.dtype or k_cache.shape != v_cache.shape \
+                    or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+                raise KernelError("projection_norm_rope_store: the caches do not match")
+            num_pages, page_size = k_cache.shape[0], k_cache.shape[2]
+        if rot_dim and (inv_freq is None or inv_freq.dtype != torch.float64 or inv_freq.numel() < rot_dim // 2):
+            raise KernelError("projection_norm_rope_store: inv_freq must be float64 [rot_dim / 2]")
+        fn = _fn("shared_kv", "iian_projection_norm_rope_store",
+                 [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+        _check(fn(pp, ld, q_off, k_off, _cuda(q_out, "q out"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"),
+                  _cuda(q_weight, "q norm weight", torch.float32), _cuda(k_weight, "k norm weight", torch.float32),
+                  _cuda(inv_freq, "inv_freq") if rot_dim else 0, _cuda(positions, "positions", torch.int32),
+                  _cuda(slots, "slots", torch.int32) if k_cache is not None else 0, _code(proj, "projections"), n, num_heads,
+                  num_kv_heads, head_dim, rot_dim, rope_style, eps, page_size, num_pages, _stream()), "projection_norm_rope_store")
+
+    def paged_attention_sink(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
+                             sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+        """Paged attention (any sizes, either dtype) whose softmax denominator also holds ``exp(sink[h])`` and whose output is
+        multiplied by ``sigmoid(gate)`` (``gate`` [N, heads * head_dim], may be a column slice); both optional."""
+        n = q.shape[0]
+        if k_cache.dtype != q.dtype or out.dtype != q.dtype or k_cache.shape != v_cache.shape:
+            raise KernelError("paged_attention_sink: q, caches and out must share one dtype and the caches one shape")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or q.numel() != n * num_heads * head_dim:
+            raise KernelError("paged_attention_sink: cache / q shapes do not match the head counts")
+        if gate is not None and (gate.shape != (n, num_heads * head_dim) or gate.dtype != q.dtype):
+            raise KernelError("paged_attention_sink: gate must be [N, heads * head_dim] in the dtype of q")
+        if sink is not None and sink.numel() != num_heads:
+            raise KernelError("paged_attention_sink: one sink per head")
+        gp, ld = self._rows(gate, "gate")
+        bt = meta.block_table
+        fn = _fn("attention_generic", "iian_paged_attention_sink",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p])
+        _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
+                  _cuda(meta.positions, "positions", torch.int32), _cuda(meta.seq_of_token, "seq_of_token", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _code(q, "q"), n, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+                  scale, window or 0, _cuda(sink, "sink", torch.float32), gp, ld, _stream()), "paged_attention_sink")
+
+    def sink_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window, sink=None,
+                       gate=None, plan=None) -> None:
+        """Attention with an optional sink and output gate, served by whichever kernel takes these sizes."""
+        self.paged_attention_sink(q, k_cache, v_cache, out, meta, num_heads=num_heads, num_kv_heads=num_kv_heads,
+                                  head_dim=head_dim, scale=scale, window=window, sink=sink, gate=gate)
+
+    # ---- the matrix-memory recurrence (csrc/matrix_memory.cu) ------------------------------------------------------------------
+    def matrix_memory_scan(self, proj: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, gate_bias: torch.Tensor,
+                           state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, *, num_heads: int,
+                           dim: int, v_dim: int, columns: int, cap: float, q_scale: float) -> None:
+        """Walk every sequence's tokens of this step through the recurrence, from and into ``state`` [slots, heads,
+        v_dim / columns, block floats] (float32).  ``proj`` rows hold q, k, v at the given column offsets; ``gates`` float32
+        [N, 2 heads] the input- and forget-gate pre-activations, ``gate_bias`` [2 heads]; ``out`` float32 [N, heads * v_dim]."""
+        n = proj.shape[0]
+        pp, ld = self._rows(proj, "projections")
+        s = cu_q.numel() - 1
+        if gates.shape != (n, 2 * num_heads) or gate_bias.numel() != 2 * num_heads or out.shape != (n, num_heads * v_dim) \
+                or state_slots.numel() != s or v_dim % columns:
+            raise KernelError("matrix_memory_scan: shapes do not fit")
+        if state.dim() != 4 or state.shape[1:] != (num_heads, v_dim // columns, self.matrix_memory_block_floats(dim, columns)):
+            raise KernelError(f"matrix_memory_scan: state {tuple(state.shape)} does not match {num_heads} heads of {dim} x {v_dim}")
+        fn = _fn("matrix_memory", "iian_matrix_memory_scan",
+                 [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+        _check(fn(pp, ld, q_off, k_off, v_off, _cuda(gates, "gates", torch.float32), _cuda(gate_bias, "gate bias", torch.float32),
+                  _cuda(state, "state", torch.float32), _cuda(cu_q, "cu_q", torch.int32), _cuda(state_slots, "state slots", torch.int32),
+                  _cuda(out, "memory out", torch.float32), _code(proj, "projections"), s, num_heads, dim, v_dim, columns, cap,
+                  q_scale, _stream()), "matrix_memory_scan")
+
+    @staticmethod
+    def matrix_memory_lanes(dim: int) -> int:
+        """Lanes that share one column of the memory in the scan kernel (csrc/matrix_memory.cu: iian_matrix_memory_lanes)."""
+        return 8 if dim <= 128 else 16 if dim <= 256 else 32
+
+    @staticmethod
+    def matrix_memory_block_floats(dim: int, columns: int) -> int:
+        """Floats of one column block of the state: the block's columns, a copy of the normaliser, the running maximum,
+        padded to a multiple of 4 (csrc/matrix_memory.cu: iian_matrix_memory_block_floats)."""
+        return ((columns + 1) * dim + 1 + 3) // 4 * 4
+
+    # ---- routing by a table, weights on the experts' outputs (csrc/moe.cu) ------------------------------------------------------
+    def moe_table_route(self, tokens: torch.Tensor, rows: Optional[torch.Tensor], table: torch.Tensor, num_experts: int,
+                        ids: torch.Tensor, weights: torch.Tensor, weight: float) -> None:
+        """``ids[r] = table[tokens[rows[r]]]`` (``rows`` None: every token in order), every weight ``weight``."""
+        n, top = ids.shape
+        if table.dim() != 2 or table.shape[1] != top or weights.shape != (n, top) or (rows is None and tokens.numel() != n) \
+                or (rows is not None and rows.numel() != n):
+            raise KernelError("moe_table_route: table [V, top]; ids / weights [N, top]")
+        fn = _fn("moe", "iian_moe_table_route", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                                                 c_int, c_void_p])
+        _check(fn(_cuda(tokens, "tokens", torch.int32), _cuda(rows, "rows", torch.int32), _cuda(table, "expert table", torch.int32),
+                  table.shape[0], num_experts, top, _cuda(ids, "expert ids", torch.int32), _cuda(weights, "expert weights", torch.float32),
+                  weight, n, tokens.numel(), _stream()), "moe_table_route")
 
     # ---- sampling ------------------------------------------------------------------------
     def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -210,6 +210,19 @@ class Head(Part):
         raise NotImplementedError
 
 
+class StreamPart(Part):
+    """A part that works on the whole residual stream between two layers (``LayerCall.before``).
+
+    ``forward(residual, delta, ctx) -> (residual, delta)``: the float32 stream and what has not been added to it yet (None, a
+    tensor, or a pair of tensors), as a block receives and returns them.  A part that reads what the embedding left says so
+    with ``needs_embedding_out``; the model then keeps that tensor untouched under ``ctx.step_cache["embedding_out"]``."""
+
+    needs_embedding_out = False
+
+    def forward(self, residual: torch.Tensor, delta, ctx):  # pragma: no cover
+        raise NotImplementedError
+
+
 class Registry:
     def __init__(self, what: str):
         self.what = what
@@ -241,6 +254,7 @@ FEED_FORWARDS = Registry("feed-forward")
 POSITIONS = Registry("position encoding")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+STREAM_PARTS = Registry("stream part")
 BLOCKS: Dict[str, type] = {}
 
 register_norm = NORMS.register
@@ -249,6 +263,7 @@ register_feed_forward = FEED_FORWARDS.register
 register_position = POSITIONS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_stream_part = STREAM_PARTS.register
 
 
 def register_block(kind: str):

@@ -95,6 +95,60 @@ class PreNormResidualBlock:
         return residual, d
 
 
+@register_block("parallel_residual")
+class ParallelResidualBlock:
+    """``h = norm(x)``; ``x += mixer(h) + ffn(h)``: ONE norm, and both sub-layers read its output.
+
+    Slots: ``mixer_norm`` (the layer's only norm), ``mixer``, optionally ``feed_forward`` (a layer without one adds the
+    mixer's output alone).  What the block hands on as ``delta`` is the PAIR (mixer output, feed-forward output): the norm
+    that comes next adds ``x + (d1 + d2)`` in float32 before it normalises, as the single-delta form does for one.
+    With ``select_rows`` (the run order's last entry) the mixer sees every row (its cache or state needs them), the
+    feed-forward only the selected ones."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        if spec.slot("mixer") is None or spec.slot("mixer_norm") is None:
+            raise ValueError("arrangement parallel_residual needs the slots mixer, mixer_norm")
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+
+    def parts(self):
+        out = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer)]
+        if self.feed_forward is not None:
+            out.append(("feed_forward", self.feed_forward))
+        return tuple(out)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, residual: torch.Tensor, delta, ctx, cache, writes_cache: bool, select_rows: Optional[torch.Tensor]):
+        h = self.mixer_norm.forward(residual, delta, ctx)        # residual += what was owed; h = norm(residual)
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        gathers = select_rows is not None and not getattr(ctx, "rows_identity", False)
+        rows = None
+        if gathers:
+            k = ops.kernels()
+            r = select_rows.shape[0]
+            res_sel = ctx.buf("residual_rows", (r, residual.shape[1]), residual.dtype)
+            y_sel = ctx.buf("mixer_out_rows", (r, y.shape[1]), y.dtype)
+            k.gather_rows(residual, select_rows, res_sel)
+            k.gather_rows(y, select_rows, y_sel)
+            residual, y = res_sel, y_sel
+            if self.feed_forward is not None:
+                h_sel = ctx.buf("normed_rows", (r, h.shape[1]), h.dtype)
+                k.gather_rows(h, select_rows, h_sel)
+                h, rows = h_sel, select_rows
+        if self.feed_forward is None:
+            return residual, y
+        if getattr(self.feed_forward, "needs_tokens", False):
+            z = self.feed_forward.forward(h, ctx, rows=rows)
+        else:
+            z = self.feed_forward.forward(h, ctx)
+        return residual, (y, z)
+
+
 class SigmoidGate:
     """A gate of a sub-layer's output: ``sigmoid(W h + b)`` per element, ``h`` the sub-layer's input.  params: ``size``.
     The matrix rides as extra rows in the sub-layer's own first product (``stack_rows``); the bias and the sigmoid are

@@ -17,12 +17,14 @@ from .base import Embedding, Head, register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``, ``hidden_size``."""
+    """params: ``vocab_size``, ``hidden_size``; optional ``scale`` (default 1): the table row is multiplied by it, in
+    float32."""
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         self.vocab = int(spec["vocab_size"])
         self.hidden = int(spec["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -32,11 +34,14 @@ class TokenEmbedding(Embedding):
         self.weight = tensors["weight"].contiguous()
 
     def kernel_libraries(self):
-        return ("elementwise",)
+        return ("elementwise",) + (("stream_ops",) if self.scale != 1.0 else ())
 
     def forward(self, tokens: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buf("residual", (tokens.shape[0], self.hidden), torch.float32)
-        ops.kernels().embedding(self.weight, tokens, out)
+        if self.scale != 1.0:
+            ops.kernels().embedding_scaled(self.weight, tokens, self.scale, out)
+        else:
+            ops.kernels().embedding(self.weight, tokens, out)
         return out
 
 

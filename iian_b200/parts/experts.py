@@ -10,6 +10,12 @@ grouped products run over the sorted rows -- gate and up with the activation in 
 kernel adds a token's expert outputs in the order of its choices.  All sizes are fixed by the number of tokens, so the
 part can be recorded into a CUDA graph.
 
+Two further forms, chosen by parameters.  ``score = "table"``: there is no router; row ``token id`` of an integer table
+[vocab, top] names the token's experts (the entries of a row differ) and every one weighs ``1 / top``.  ``weight_on =
+"output"``: the weight multiplies what the expert returns, ``y = sum_e w_e expert_e(h)``.  ``activation =
+"clamped_swish"``: ``g = min(Wgate u, limit)``, ``v = clamp(Wup u, -limit, limit)``, the expert's hidden row is
+``g sigmoid(1.702 g) (v + 1)``.
+
 ``stack_rows`` puts further rows that read the same input (a gate of the residual) under the router's, so that one
 product with float32 output serves both.
 """
@@ -27,7 +33,10 @@ from .base import FeedForward, register_feed_forward
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
     """params: ``hidden_size``, ``num_experts``, ``top``, ``intermediate_size`` (of one expert), ``activation``
-    (``silu`` | ``gelu_tanh``), ``score`` (``sigmoid``), ``weight_on`` (``input``)."""
+    (``silu`` | ``gelu_tanh`` | ``clamped_swish`` with ``limit``), ``score`` (``sigmoid`` | ``table`` with ``vocab_size``),
+    ``weight_on`` (``input`` | ``output``)."""
+
+    SWISH_ALPHA = 1.702         # fixed by the clamped activation (also in the kernels)
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -37,17 +46,28 @@ class RoutedExperts(FeedForward):
         self.top = int(p["top"])
         self.inter = int(p["intermediate_size"])
         self.activation = p.get("activation", "silu")
-        if self.activation not in ("silu", "gelu_tanh"):
+        if self.activation not in ("silu", "gelu_tanh", "clamped_swish"):
             raise ValueError(f"routed_experts: activation '{self.activation}' has no kernel")
-        if p.get("score", "sigmoid") != "sigmoid" or p.get("weight_on", "input") != "input":
-            raise ValueError("routed_experts: sigmoid scores that weigh the expert's input are what is built")
+        self.limit = float(p.get("limit", 0.0))
+        if self.activation == "clamped_swish" and self.limit <= 0:
+            raise ValueError("routed_experts: the clamped activation needs a positive limit")
+        self.score = p.get("score", "sigmoid")
+        self.weight_on = p.get("weight_on", "input")
+        if self.score not in ("sigmoid", "table") or self.weight_on not in ("input", "output"):
+            raise ValueError("routed_experts: score is 'sigmoid' or 'table', weight_on 'input' or 'output'")
+        self.vocab = int(p["vocab_size"]) if self.score == "table" else 0
+        self.needs_tokens = self.score == "table"       # forward wants to know which token each row belongs to
         if not 0 < self.top <= self.experts:
             raise ValueError(f"routed_experts: top {self.top} of {self.experts} experts")
         self.w_router = self.w_gate = self.w_up = self.w_down = self.w_gate_up = None
         self.extra_rows = None
+        self.table = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        t = {"router": TensorSpec((self.experts, self.hidden))}
+        if self.score == "table":
+            t = {"table": TensorSpec((self.vocab, self.top), kind="int", init=f"distinct_rows:{self.experts}")}
+        else:
+            t = {"router": TensorSpec((self.experts, self.hidden))}
         for e in range(self.experts):
             t[f"e{e}.gate"] = TensorSpec((self.inter, self.hidden))
             t[f"e{e}.up"] = TensorSpec((self.inter, self.hidden))
@@ -55,8 +75,11 @@ class RoutedExperts(FeedForward):
         return t
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self._router = tensors["router"]
-        self.w_router = self._router.contiguous()
+        if self.score == "table":
+            self.table = tensors["table"].to(torch.int32).contiguous()
+        else:
+            self._router = tensors["router"]
+            self.w_router = self._router.contiguous()
         gate = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)])
         up = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)])
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
@@ -69,6 +92,8 @@ class RoutedExperts(FeedForward):
             self.w_gate_up, self.w_gate, self.w_up = None, gate.contiguous(), up.contiguous()
 
     def stack_rows(self, rows: torch.Tensor) -> None:
+        if self.score == "table":
+            raise ValueError("routed_experts: without a router there is no product to carry further rows")
         self.extra_rows = rows
         ws = [self._router, rows]
         if ws[0].dtype != ws[1].dtype:
@@ -78,7 +103,9 @@ class RoutedExperts(FeedForward):
     def kernel_libraries(self):
         return ("moe", "gemm_simt")        # in bfloat16 the products' fast forms come with gemm_simt (the grouped tcgen05 one too)
 
-    def forward(self, x, ctx, with_extra: bool = False):
+    def forward(self, x, ctx, with_extra: bool = False, rows=None):
+        """``rows`` (int32, optional): the step's token each row of ``x`` belongs to, when ``x`` holds selected rows only
+        (a part with ``needs_tokens`` is told; without it row r is token r)."""
         k = ops.kernels()
         n = x.shape[0]
         top, E = self.top, self.experts
@@ -86,11 +113,16 @@ class RoutedExperts(FeedForward):
         if n == 0:
             out = ctx.buf("ffn_out", (0, self.hidden), self.dtype)
             return (out, None) if with_extra else out
-        logits = ctx.buf("router_logits", (n, self.w_router.shape[0]), torch.float32)
-        k.linear(x, self.w_router, logits)
         ids = ctx.buf("expert_ids", (n, top), torch.int32)
         wts = ctx.buf("expert_weights", (n, top), torch.float32)
-        k.moe_route(logits[:, :E], top, ids, wts)
+        logits = None
+        if self.score == "table":
+            k.moe_table_route(ctx.tokens, rows, self.table, E, ids, wts, 1.0 / top)
+        else:
+            logits = ctx.buf("router_logits", (n, self.w_router.shape[0]), torch.float32)
+            k.linear(x, self.w_router, logits)
+            k.moe_route(logits[:, :E], top, ids, wts)
+        on_input = self.weight_on == "input"
         on_tc = (self.w_gate_up is not None and hasattr(k, "moe_tcgen05_ok")
                  and k.moe_tcgen05_ok(self.dtype, self.hidden, self.inter, self.activation))
         tile_rows = k.MOE_TC_TILE_ROWS if on_tc else k.moe_tile_rows()
@@ -100,7 +132,7 @@ class RoutedExperts(FeedForward):
         tiles = ctx.buf("expert_tiles", (1 + 2 * max_tiles,), torch.int32)
         k.moe_plan(ids, E, offsets, pos, tiles, tile_rows)
         xs = ctx.buf("expert_in", (m, self.hidden), self.dtype)
-        k.moe_scatter(x, pos, wts, xs, top)
+        k.moe_scatter(x, pos, wts if on_input else None, xs, top)
         act = ctx.buf("expert_act", (m, self.inter), self.dtype)
         ys = ctx.buf("expert_out", (m, self.hidden), self.dtype)
         if on_tc:
@@ -108,12 +140,15 @@ class RoutedExperts(FeedForward):
             k.moe_grouped_gemm_tc(act, self.w_down, ys, offsets, tiles, gated=False)
         else:
             if self.w_gate_up is not None:
-                k.moe_grouped_gemm(xs, self.w_gate_up, self.w_gate_up, act, offsets, tiles, self.activation)
+                k.moe_grouped_gemm(xs, self.w_gate_up, self.w_gate_up, act, offsets, tiles, self.activation, self.limit)
             else:
-                k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation)
+                k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation, self.limit)
             k.moe_grouped_gemm(act, self.w_down, None, ys, offsets, tiles)
         out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
-        k.moe_combine(ys, pos, out, top)
+        if on_input:
+            k.moe_combine(ys, pos, out, top)
+        else:
+            k.moe_combine(ys, pos, out, top, wts)
         if with_extra:
             return out, (logits[:, E:] if self.extra_rows is not None else None)
         return out

@@ -17,19 +17,25 @@ from .base import Norm, register_norm
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``."""
+    """params: ``size``, ``eps``; optional ``weight_offset`` (default 0): the stored weight ``w`` is used as
+    ``weight_offset + w`` (a weight kept around zero has ``weight_offset`` 1).
+
+    ``delta`` may be a pair of tensors (the outputs of two sub-layers that read the same norm): the stream becomes
+    ``x + (d1 + d2)``, summed in float32."""
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.offset = float(spec.params.get("weight_offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), init="ones_jitter")}
+        return {"weight": TensorSpec((self.size,), init="zeros_jitter" if self.offset else "ones_jitter")}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].to(torch.float32).contiguous()     # exact widening; the kernel multiplies in float32
+        w = tensors["weight"].to(torch.float32)                            # exact widening; the kernel multiplies in float32
+        self.weight = (w + self.offset if self.offset else w).contiguous()
 
     def kernel_libraries(self):
         return ("elementwise",)
@@ -37,8 +43,14 @@ class RMSNorm(Norm):
     def foldable(self):
         return (self.weight, self.eps) if self.weight is not None else None
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
+    def forward(self, residual: torch.Tensor, delta, ctx) -> torch.Tensor:
         out = ctx.buf("normed", residual.shape, self.dtype)
+        if isinstance(delta, tuple):
+            live = [d for d in delta if d is not None]
+            if len(live) == 2:
+                ops.kernels().add2_rms_norm(residual, live[0], live[1], self.weight, self.eps, out)
+                return out
+            delta = live[0] if live else None
         ops.kernels().add_rms_norm(residual, delta, self.weight, self.eps, out)
         return out
 

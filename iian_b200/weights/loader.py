@@ -27,7 +27,8 @@ class TensorSpec:
     shape: Tuple[int, ...]
     optional: bool = False
     kind: str = "float"
-    init: str = "normal"          # how the random-weights mode fills it: normal | ones_jitter | zeros
+    init: str = "normal"          # how the random-weights mode fills it: normal | ones_jitter | zeros_jitter | zeros;
+                                  # integer tables: zeros, or "distinct_rows:<n>" (every row distinct values below n)
 
 
 class WeightsError(ValueError):

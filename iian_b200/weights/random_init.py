@@ -21,6 +21,7 @@ bits differ between CPU and GPU libraries); the tails end near 4.3 standard devi
 from __future__ import annotations
 
 import json
+import math
 import os
 from typing import Dict, Mapping, Optional
 
@@ -106,6 +107,16 @@ def standard_normal(key: int, start: int, count: int, device: torch.device) -> t
 def draw(name: str, spec: TensorSpec, seed: int, device: torch.device, std: float, jitter: float) -> torch.Tensor:
     """One tensor in float32 on ``device``."""
     if spec.kind == "int":
+        if spec.init.startswith("distinct_rows:"):
+            # row r: `cols` different values below n -- a start drawn per row, then steps of a stride coprime to n
+            n = int(spec.init.split(":", 1)[1])
+            rows, cols = spec.shape
+            if cols > n:
+                raise ValueError(f"{name}: {cols} distinct values below {n} do not exist")
+            bits = _lsr(element_bits(tensor_key(seed, name), 0, rows, device), 8)
+            stride = next(s for s in range(max(1, n // 3), n + 1) if math.gcd(s, n) == 1) if n > 1 else 1
+            j = torch.arange(cols, dtype=torch.int64, device=device)
+            return ((bits % n)[:, None] + j[None, :] * stride).remainder(n).to(torch.int32)
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=torch.float32, device=device)
@@ -115,8 +126,8 @@ def draw(name: str, spec: TensorSpec, seed: int, device: torch.device, std: floa
     step = 1 << 24                                  # slabs bound the temporary memory (a few hundred MB)
     for s in range(0, flat.numel(), step):
         n = min(step, flat.numel() - s)
-        if spec.init == "ones_jitter":
-            flat[s:s + n] = 1.0 + (2.0 * uniform(key, s, n, device) - 1.0) * jitter
+        if spec.init in ("ones_jitter", "zeros_jitter"):
+            flat[s:s + n] = (1.0 if spec.init == "ones_jitter" else 0.0) + (2.0 * uniform(key, s, n, device) - 1.0) * jitter
         else:
             flat[s:s + n] = standard_normal(key, s, n, device) * std
     return t
@@ -149,7 +160,7 @@ class RandomWeights(WeightSource):
         """Matrices in ``store_dtype``; norm weights in float32 (a tensor stored in 32 bits)."""
         if spec.kind == "int":
             return torch.int32
-        return torch.float32 if spec.init == "ones_jitter" else self.store_dtype
+        return torch.float32 if spec.init in ("ones_jitter", "zeros_jitter") else self.store_dtype
 
     def fetch(self, name: str, spec: TensorSpec, compute: torch.dtype, device: torch.device) -> torch.Tensor:
         t = draw(name, spec, self.seed, device, self.std, self.norm_jitter)

@@ -27,6 +27,139 @@ class FakeKernels:
         x = residual
         out.copy_((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
 
+    def embedding_scaled(self, table, tokens, scale, out):
+        out.copy_(table[tokens.long()].float() * scale)
+
+    def add2_rms_norm(self, residual, delta, delta2, weight, eps, out):
+        residual.add_(delta.float() + delta2.float())
+        self.add_rms_norm(residual, None, weight, eps, out)
+
+    def stream_concat(self, x, d1, d2, e, out):
+        v = x.clone()
+        if d1 is not None and d2 is not None:
+            v += d1.float() + d2.float()
+        elif d1 is not None or d2 is not None:
+            v += (d1 if d1 is not None else d2).float()
+        out.copy_(torch.cat([v, e], dim=-1).to(out.dtype))
+
+    def sigmoid_mul(self, x, gate, out):
+        out.copy_((x.float() * torch.sigmoid(gate.float())).to(out.dtype))
+
+    def head_norm_gate(self, x, weight, gate, out, *, num_heads, eps):
+        n, m = x.shape
+        v = x.view(n, num_heads, m // num_heads)
+        v = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(n, m) * weight
+        if gate is not None:
+            v = v * torch.sigmoid(gate.float())
+        out.copy_(v.to(out.dtype))
+
+    def projection_norm_rope_store(self, proj, q_off, k_off, q_out, k_cache, v_cache, *, num_heads, num_kv_heads, head_dim,
+                                   q_weight, k_weight, eps, inv_freq, rot_dim, rope_style, positions, slots):
+        n = proj.shape[0]
+        q = proj[:, q_off:q_off + num_heads * head_dim].float()
+        kraw = proj[:, k_off:k_off + num_kv_heads * head_dim]
+        k = kraw.float()
+        if q_weight is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_weight
+            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_weight
+
+        def rope(t):
+            if not rot_dim:
+                return t
+            th = positions.double()[:, None] * inv_freq.double()[None, : rot_dim // 2]
+            cos, sin = torch.cos(th).float()[:, None, :], torch.sin(th).float()[:, None, :]
+            o = t.clone()
+            half = rot_dim // 2
+            if rope_style == 0:
+                a, b = t[..., :half], t[..., half:rot_dim]
+                o[..., :half] = a * cos - b * sin
+                o[..., half:rot_dim] = a * sin + b * cos
+            else:
+                a, b = t[..., 0:rot_dim:2], t[..., 1:rot_dim:2]
+                o[..., 0:rot_dim:2] = a * cos - b * sin
+                o[..., 1:rot_dim:2] = a * sin + b * cos
+            return o
+
+        q_out.view(n, num_heads, head_dim).copy_(rope(q.view(n, num_heads, head_dim)).to(q_out.dtype))
+        if k_cache is not None:
+            k = rope(k.view(n, num_kv_heads, head_dim))
+            v = kraw.reshape(n, num_kv_heads, head_dim)
+            ps = k_cache.shape[2]
+            for t in range(n):
+                s = int(slots[t])
+                if s < 0:
+                    continue
+                k_cache[s // ps, :, s % ps, :] = k[t].to(k_cache.dtype)
+                v_cache[s // ps, :, s % ps, :] = v[t].to(v_cache.dtype)
+
+    def sink_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window, sink=None,
+                       gate=None, plan=None):
+        n = q.shape[0]
+        ps = k_cache.shape[2]
+        g = num_heads // num_kv_heads
+        qf = q.float().view(n, num_heads, head_dim)
+        o = torch.zeros(n, num_heads, head_dim)
+        for t in range(n):
+            s = int(meta.seq_of_token[t])
+            if s < 0:
+                continue
+            p = int(meta.positions[t])
+            lo = max(0, p - window + 1) if window else 0
+            js = torch.arange(lo, p + 1)
+            pages = meta.block_table[s, (js // ps).long()].long()
+            assert (pages >= 0).all(), "attention reads a page that was given back"
+            kk = k_cache[pages, :, (js % ps).long(), :].float()
+            vv = v_cache[pages, :, (js % ps).long(), :].float()
+            for h in range(num_heads):
+                sc = (kk[:, h // g, :] @ qf[t, h]) * scale
+                if sink is not None:
+                    sc = torch.cat([sc, sink[h:h + 1]])
+                pr = torch.softmax(sc, dim=0)[: js.numel()]
+                o[t, h] = pr @ vv[:, h // g, :]
+        o = o.view(n, num_heads * head_dim)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float())
+        out.copy_(o.to(out.dtype))
+
+    def matrix_memory_scan(self, proj, q_off, k_off, v_off, gates, gate_bias, state, cu_q, state_slots, out, *, num_heads, dim,
+                           v_dim, columns, cap, q_scale):
+        H, d, dv, cb = num_heads, dim, v_dim, columns
+        nblk = dv // cb
+        for s in range(state_slots.numel()):
+            t0, t1, slot = int(cu_q[s]), int(cu_q[s + 1]), int(state_slots[s])
+            if slot < 0:
+                out[t0:t1] = 0
+                continue
+            if t1 <= t0:
+                continue
+            st = state[slot]                                            # [H, nblk, block floats]
+            C = st[:, :, : cb * d].reshape(H, nblk, cb, d).permute(0, 3, 1, 2).reshape(H, d, dv).clone()
+            nn = st[:, 0, cb * d:(cb + 1) * d].clone()
+            m = st[:, 0, (cb + 1) * d].clone()
+            for t in range(t0, t1):
+                row = proj[t].float()
+                q = row[q_off:q_off + H * d].view(H, d) * q_scale
+                k = row[k_off:k_off + H * d].view(H, d)
+                v = row[v_off:v_off + H * dv].view(H, dv)
+                z = gates[t] + gate_bias
+                a = cap * torch.tanh(z[:H] / cap)
+                b = torch.nn.functional.logsigmoid(cap * torch.tanh(z[H:] / cap))
+                m_new = torch.maximum(b + m, a)
+                keep, take = torch.exp(b + m - m_new), torch.exp(a - m_new)
+                C = keep[:, None, None] * C + take[:, None, None] * k[:, :, None] * v[:, None, :]
+                nn = keep[:, None] * nn + take[:, None] * k
+                m = m_new
+                den = torch.maximum((nn * q).sum(-1).abs(), torch.exp(-m)) + 1e-6
+                out[t] = (torch.einsum("hdv,hd->hv", C, q) / den[:, None]).reshape(-1)
+            st[:, :, : cb * d] = C.view(H, d, nblk, cb).permute(0, 2, 3, 1).reshape(H, nblk, cb * d)
+            st[:, :, cb * d:(cb + 1) * d] = nn[:, None, :]
+            st[:, :, (cb + 1) * d] = m[:, None]
+
+    def moe_table_route(self, tokens, rows, table, num_experts, ids, weights, weight):
+        t = tokens.long() if rows is None else tokens.long()[rows.long()]
+        ids.copy_(table[t])
+        weights.fill_(weight)
+
     def rms_norm(self, x, weight, eps, out):
         xf = x.float()
         out.copy_((xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
@@ -238,11 +371,11 @@ class FakeKernels:
         offsets[1:] = torch.cumsum(counts, 0).int()
 
     def moe_scatter(self, h, pos, weights, xs, top):
-        w = weights.reshape(-1)
+        w = weights.reshape(-1) if weights is not None else torch.ones(pos.numel())
         for i in range(pos.numel()):
             xs[int(pos[i])] = (w[i] * h[i // top].float()).to(xs.dtype)
 
-    def moe_grouped_gemm(self, x, w, w2, out, offsets, tiles, activation="silu"):
+    def moe_grouped_gemm(self, x, w, w2, out, offsets, tiles, activation="silu", limit=0.0):
         if w2 is w:         # gate and up interleaved in groups of 8 rows
             v = w.view(w.shape[0], w.shape[1] // 16, 2, 8, w.shape[2])
             w, w2 = v[:, :, 0].reshape(w.shape[0], -1, w.shape[2]), v[:, :, 1].reshape(w.shape[0], -1, w.shape[2])
@@ -252,11 +385,19 @@ class FakeKernels:
                 continue
             y = x[a:b].float() @ w[e].float().T
             if w2 is not None:
-                y = self._act(y.to(out.dtype).float(), activation) * (x[a:b].float() @ w2[e].float().T).to(out.dtype).float()
+                g, u = y.to(out.dtype).float(), (x[a:b].float() @ w2[e].float().T).to(out.dtype).float()
+                if activation == "clamped_swish":
+                    g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+                    y = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+                else:
+                    y = self._act(g, activation) * u
             out[a:b] = y.to(out.dtype)
 
-    def moe_combine(self, ys, pos, out, top):
-        out.copy_(ys[pos.long()].float().view(out.shape[0], top, -1).sum(1).to(out.dtype))
+    def moe_combine(self, ys, pos, out, top, weights=None):
+        y = ys[pos.long()].float().view(out.shape[0], top, -1)
+        if weights is not None:
+            y = y * weights.view(out.shape[0], top, 1)
+        out.copy_(y.sum(1).to(out.dtype))
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).int())
