@@ -28,6 +28,18 @@ def load_folder(model_dir: str):
 
 
 # ---- elementary pieces ------------------------------------------------------------------------------
+# What a matrix product's result passes through before anything else reads it: nothing.  A test that wants to know how far
+# 16-bit products alone move the logits sets this to a rounding function for the time of a call.
+product_rounding = None
+
+
+def mm(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``h W^T`` (weights are stored [out, in]); with ``product_rounding`` set, its input and its result pass through it."""
+    if product_rounding is None:
+        return h @ w.T
+    return product_rounding(product_rounding(h) @ w.T)
+
+
 def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
@@ -80,8 +92,8 @@ def shared_kv_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str
     """Attention whose values are the keys as projected.  ``h`` [T, W]."""
     T = h.shape[0]
     H, G, d = mc["heads"], mc["kv_heads"], mc["dim"]
-    q = h @ t[pre + "q"].T                                     # [T, H d]
-    k = h @ t[pre + "k"].T                                     # [T, G d]
+    q = mm(h, t[pre + "q"])                                     # [T, H d]
+    k = mm(h, t[pre + "k"])                                     # [T, G d]
     v = k.view(T, G, d)                                        # the values: the keys before norm and rotation
     q = unit_rms(q, eps) * t[pre + "q.norm"]                   # one norm over the whole projection, all heads at once
     k = unit_rms(k, eps) * t[pre + "k.norm"]
@@ -100,8 +112,8 @@ def shared_kv_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str
     else:
         p = torch.softmax(scores.masked_fill(~vis[None], float("-inf")), -1)
     o = torch.einsum("hij,jhd->ihd", p, v[:, group]).reshape(T, H * d)
-    o = o * torch.sigmoid(h @ t[pre + "g"].T)
-    return o @ t[pre + "o"].T
+    o = o * torch.sigmoid(mm(h, t[pre + "g"]))
+    return mm(o, t[pre + "o"])
 
 
 def soft_cap(z: torch.Tensor, cap: float) -> torch.Tensor:
@@ -122,11 +134,11 @@ def matrix_memory(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, mc: 
     T = h.shape[0]
     H, d, dv = mc["heads"], mc["dim"], mc["vdim"]
     cap = mc["gate_cap"]
-    q = (h @ t[pre + "q"].T).view(T, H, d) * d ** -0.5
-    k = (h @ t[pre + "k"].T).view(T, H, d)
-    v = (h @ t[pre + "v"].T).view(T, H, dv)
-    a = soft_cap(h @ t[pre + "i"].T + t[pre + "i.b"], cap)                                    # [T, H]
-    b = torch.nn.functional.logsigmoid(soft_cap(h @ t[pre + "f"].T + t[pre + "f.b"], cap))
+    q = mm(h, t[pre + "q"]).view(T, H, d) * d ** -0.5
+    k = mm(h, t[pre + "k"]).view(T, H, d)
+    v = mm(h, t[pre + "v"]).view(T, H, dv)
+    a = soft_cap(mm(h, t[pre + "i"]) + t[pre + "i.b"], cap)                                    # [T, H]
+    b = torch.nn.functional.logsigmoid(soft_cap(mm(h, t[pre + "f"]) + t[pre + "f.b"], cap))
     if state is None:
         C = torch.zeros(H, d, dv, dtype=h.dtype)
         n = torch.zeros(H, d, dtype=h.dtype)
@@ -145,20 +157,20 @@ def matrix_memory(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, mc: 
         den = torch.maximum((n * q[s]).sum(-1).abs(), torch.exp(-m)) + 1e-6
         out[s] = num / den[:, None]
     out = unit_rms(out, eps).reshape(T, H * dv) * t[pre + "norm"]          # each head by its own root mean square
-    out = out * torch.sigmoid(h @ t[pre + "g"].T)
-    y = out @ t[pre + "o"].T
+    out = out * torch.sigmoid(mm(h, t[pre + "g"]))
+    y = mm(out, t[pre + "o"])
     return (y, (C, n, m)) if return_state else y
 
 
 # ---- feed-forwards ------------------------------------------------------------------------------------------
 def dense_ff(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str) -> torch.Tensor:
-    return (silu(h @ t[pre + "gate"].T) * (h @ t[pre + "up"].T)) @ t[pre + "down"].T
+    return mm(silu(mm(h, t[pre + "gate"])) * mm(h, t[pre + "up"]), t[pre + "down"])
 
 
 def clamped_expert(h: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, limit: float) -> torch.Tensor:
-    g = torch.clamp(h @ t[pre + "gate"].T, max=limit)
-    u = torch.clamp(h @ t[pre + "up"].T, -limit, limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ t[pre + "down"].T
+    g = torch.clamp(mm(h, t[pre + "gate"]), max=limit)
+    u = torch.clamp(mm(h, t[pre + "up"]), -limit, limit)
+    return mm(g * torch.sigmoid(1.702 * g) * (u + 1.0), t[pre + "down"])
 
 
 def table_routed_ff(h: torch.Tensor, tokens: torch.Tensor, t: Mapping[str, torch.Tensor], pre: str, fc: Mapping) -> torch.Tensor:
@@ -197,7 +209,7 @@ def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], tokens, dtype=tor
     for i, starts_run in run_order(cfg):
         lc = cfg["layers"][i]
         if starts_run:
-            x = torch.cat([x, e], dim=-1) @ t["loop.in"].T
+            x = mm(torch.cat([x, e], dim=-1), t["loop.in"])
         h = offset_rms_norm(x, t[f"l{i}.norm1"], eps)
         if lc["type"] == "attention":
             y = shared_kv_attention(h, t, f"l{i}.mix.", lc["mixer"], eps)
@@ -210,5 +222,5 @@ def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], tokens, dtype=tor
             y = y + (dense_ff(h, t, f"l{i}.mlp.") if fc["kind"] == "dense" else table_routed_ff(h, tokens, t, f"l{i}.mlp.", fc))
         x = x + y
         layers.append(x)
-    logits = offset_rms_norm(x, t["final.norm"], eps) @ t["head"].T
+    logits = mm(offset_rms_norm(x, t["final.norm"], eps), t["head"])
     return (logits, torch.stack(layers)) if return_layers else logits
