@@ -51,6 +51,9 @@ struct AttnParams {
     float eps;
     int write_kv;
     int * status;                   // TMA form of the decode kernel: {code, where}, zero before the launch
+    // a sink per head: a logit without key and value that joins the softmax's denominator once, not scaled
+    const float * sink = nullptr;   // [nh] or null
+    float sink_to_raw = 0.0f;       // 1 / scale: the kernels keep maxima of raw scores and scale in the exponent
 };
 
 // Tensor maps of the K and V caches for the TMA form of the decode kernel (unused by the other forms).
@@ -217,6 +220,17 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
         const int R = row0 + warp * 16 + g_ + 8 * h;
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);       // position of the row's token
+    }
+    if (p.sink != nullptr && split == 0) {
+        // the running softmax of a row starts at the sink: maximum sink, sum 1 (the sum is kept in parts over the quad)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int R = row0 + warp * 16 + g_ + 8 * h;
+            if (R < rows_total) {
+                m_run[h] = p.sink[kvh * G + R % G] * p.sink_to_raw;
+                l_run[h] = t_ == 0 ? 1.0f : 0.0f;
+            }
+        }
     }
     // bounds over the 16 rows of this warp: tiles wholly below every row's diagonal need no mask
     const int wr0 = row0 + warp * 16, wr1 = min(rows_total - 1, wr0 + 15);
@@ -541,6 +555,17 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
         const int R = row0 + g_ + 8 * h;
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);
+    }
+    if (p.sink != nullptr && split == 0 && warp == 0) {
+        // the sink counts once: in the first warp of the first part (the merges weigh it like any other part)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int R = row0 + g_ + 8 * h;
+            if (R < rows_total) {
+                m_run[h] = p.sink[kvh * G + R % G] * p.sink_to_raw;
+                l_run[h] = t_ == 0 ? 1.0f : 0.0f;
+            }
+        }
     }
     const int pos_min = pos0 + tok_min, pos_max = pos0 + tok_max;
     const bool rows_full = row0 + BM <= rows_total;
@@ -1092,12 +1117,30 @@ IIAN_API int iian_attention_decode_stages(int stages) {
     return IIAN_OK;
 }
 
+IIAN_API int iian_attention_mma_sink(
+    const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int n_split, int small_tiles, int * status, const float * sink, cudaStream_t stream);
+
 IIAN_API int iian_attention_mma(
     const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
     int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int n_split, int small_tiles, int * status, cudaStream_t stream) {
+    return iian_attention_mma_sink(q, k_cache, v_cache, out, part_o, part_lse, counters, cu_q, ctx_len, block_table, max_blocks, N, S,
+                                   max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, n_split, small_tiles, status, nullptr,
+                                   stream);
+}
+
+// The same with a sink per head in the softmax's denominator (sink: f32 [nh], or null; needs scale > 0).
+IIAN_API int iian_attention_mma_sink(
+    const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int n_split, int small_tiles, int * status, const float * sink, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
+    if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
     const bool cluster = small_tiles == 2 && n_split > 1;   // decode form, parts merged inside a thread-block cluster
@@ -1114,6 +1157,8 @@ IIAN_API int iian_attention_mma(
     p.k_cache_w = nullptr; p.v_cache_w = nullptr; p.qkv = nullptr; p.q_weight = nullptr; p.k_weight = nullptr;
     p.table = nullptr; p.slots = nullptr; p.eps = 0.0f; p.write_kv = 0;
     p.status = ((uintptr_t) k_cache & 15) || ((uintptr_t) v_cache & 15) ? nullptr : status;
+    p.sink = sink;
+    p.sink_to_raw = sink != nullptr ? 1.0f / scale : 0.0f;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
     if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);

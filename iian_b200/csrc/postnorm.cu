@@ -203,7 +203,7 @@ __device__ __forceinline__ float act_apply(float z, int act) {
 // values of the same features (interleave 8); row stride ld_in elements
 template <typename A>
 __global__ void gated_act_kernel(const A * __restrict__ in, long long ld_in, A * __restrict__ out, int F, size_t total,
-                                 int interleave, int act) {
+                                 int interleave, int act, float limit) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t idx = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
@@ -212,7 +212,14 @@ __global__ void gated_act_kernel(const A * __restrict__ in, long long ld_in, A *
     const int col = (int) (idx - r * F);
     const size_t gi = r * ld_in + (interleave ? (size_t) (col / 8) * 16 + col % 8 : (size_t) col);
     const size_t ui = interleave ? gi + 8 : gi + F;
-    out[idx] = from_f32<A>(act_apply(to_f32(in[gi]), act) * to_f32(in[ui]));
+    float g = to_f32(in[gi]), u = to_f32(in[ui]);
+    if (act == 2) {     // clamped: g' = min(g, limit), u' = clamp(u, -limit, limit); g' sigmoid(1.702 g') (u' + 1)
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        out[idx] = from_f32<A>(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+        return;
+    }
+    out[idx] = from_f32<A>(act_apply(g, act) * u);
 }
 
 }  // namespace iian
@@ -281,16 +288,26 @@ IIAN_API int iian_depth_mix(const float * const * terms, int n_terms, const floa
     return IIAN_ERR_DTYPE;
 }
 
+IIAN_API int iian_gated_act_limit(const void * in, long long ld_in, void * out, int act_dtype, int N, int F, int interleave, int act,
+                                  float limit, cudaStream_t stream);
+
 // act: 0 silu, 1 gelu (tanh form)
 IIAN_API int iian_gated_act(const void * in, long long ld_in, void * out, int act_dtype, int N, int F, int interleave, int act,
                             cudaStream_t stream) {
-    if (interleave != 0 && (interleave != 8 || F % 8 != 0)) return IIAN_ERR_SHAPE;
     if (act != 0 && act != 1) return IIAN_ERR_SHAPE;
+    return iian_gated_act_limit(in, ld_in, out, act_dtype, N, F, interleave, act, 0.0f, stream);
+}
+
+// act: 0 silu, 1 gelu (tanh form), 2 clamped (takes `limit`)
+IIAN_API int iian_gated_act_limit(const void * in, long long ld_in, void * out, int act_dtype, int N, int F, int interleave, int act,
+                                  float limit, cudaStream_t stream) {
+    if (interleave != 0 && (interleave != 8 || F % 8 != 0)) return IIAN_ERR_SHAPE;
+    if (act < 0 || act > 2) return IIAN_ERR_SHAPE;
     const size_t total = (size_t) N * F;
     if (total == 0) return IIAN_OK;
     const int threads = 256;
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
-    if (act_dtype == IIAN_F32) return iian_launch(gated_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) in, ld_in, (float *) out, F, total, interleave, act);
-    if (act_dtype == IIAN_BF16) return iian_launch(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) in, ld_in, (__nv_bfloat16 *) out, F, total, interleave, act);
+    if (act_dtype == IIAN_F32) return iian_launch(gated_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) in, ld_in, (float *) out, F, total, interleave, act, limit);
+    if (act_dtype == IIAN_BF16) return iian_launch(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) in, ld_in, (__nv_bfloat16 *) out, F, total, interleave, act, limit);
     return IIAN_ERR_DTYPE;
 }

@@ -725,8 +725,9 @@ class CudaKernels:
 
     def paged_attention_mma(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
                             n_split: Optional[int] = None, small_tiles: Optional[bool] = None,
-                            cluster: Optional[bool] = None) -> None:
-        """``small_tiles``: the decode form (rows of one token, keys split over the warps); ``cluster``: its
+                            cluster: Optional[bool] = None, sink: Optional[torch.Tensor] = None) -> None:
+        """``sink``: float32 [heads], a logit per head that joins the softmax's denominator (needs ``scale`` > 0).
+        ``small_tiles``: the decode form (rows of one token, keys split over the warps); ``cluster``: its
         parts merge through the shared memory of a thread-block cluster (2, 4 or 8 parts) instead of scratch
         memory.  None: chosen from the step."""
         n = q.shape[0]
@@ -754,15 +755,18 @@ class CudaKernels:
                 row_tiles = -(-meta.max_q_len * (num_heads // num_kv_heads) // 16)
                 counters = self.attention_counters(q.device, meta.num_seqs * num_kv_heads * row_tiles).data_ptr()
         bt = meta.block_table
-        fn = _fn("attention_mma", "iian_attention_mma",
+        if sink is not None and sink.numel() != num_heads:
+            raise KernelError("paged_attention_mma: one sink per head")
+        fn = _fn("attention_mma", "iian_attention_mma_sink",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+                  c_void_p])
         _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, n_split,
                   (2 if cluster else 1) if small_tiles else 0, self._decode_status(q.device) if small_tiles else None,
-                  _stream()), "attention_mma")
+                  _cuda(sink, "sink", torch.float32), _stream()), "attention_mma")
         if n_split > 1 and not small_tiles:
             LAUNCHES[0] += 1
 
@@ -903,15 +907,16 @@ class CudaKernels:
 
     ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
-    def gated_act(self, gate_up: torch.Tensor, out: torch.Tensor, interleave: int, activation: str) -> None:
-        """``out = act(gate) * up`` for rows ``[gate | up]`` (or interleaved in groups of 8); ``gate_up`` may be a column slice."""
+    def gated_act(self, gate_up: torch.Tensor, out: torch.Tensor, interleave: int, activation: str, limit: float = 0.0) -> None:
+        """``out = act(gate) * up`` for rows ``[gate | up]`` (or interleaved in groups of 8); ``gate_up`` may be a column slice.
+        ``clamped_swish`` (with ``limit``): ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``g sigmoid(1.702 g) (u + 1)``."""
         n, f2 = gate_up.shape
         if out.shape != (n, f2 // 2) or f2 % 2 or out.dtype != gate_up.dtype:
             raise KernelError("gated_act: out must be [N, F] for gate_up [N, 2F] of the same dtype")
         gp, ld = self._rows(gate_up, "gate_up")
-        fn = _fn("postnorm", "iian_gated_act", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        fn = _fn("postnorm", "iian_gated_act_limit", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
         _check(fn(gp, ld, _cuda(out, "gated_act out"), _code(out, "gated_act out"), n, f2 // 2, interleave,
-                  self.ACTIVATIONS[activation], _stream()), "gated_act")
+                  self.ACTIVATIONS[activation], limit, _stream()), "gated_act")
 
     # ---- attention over a cached latent (csrc/latent_attention.cu) ------------------------------------------------
     def latent_prep(self, qd: torch.Tensor, q_off: int, dkv_off: int, cache_rows: Optional[torch.Tensor], q_cat: torch.Tensor,
@@ -1076,9 +1081,10 @@ class CudaKernels:
 
     def moe_tcgen05_ok(self, dtype: torch.dtype, hidden: int, inter: int, activation: str) -> bool:
         """Whether both grouped products of an expert feed-forward can run on the tcgen05 kernel: bfloat16, rows of 16
-        bytes' multiples for TMA, gate and up interleaved in groups of 8 with the SiLU epilogue."""
-        return (self.MOE_TCGEN05 and not self.LIBRARY_GEMM_ONLY and dtype == torch.bfloat16 and activation == "silu"
-                and hidden % 8 == 0 and inter % 8 == 0)
+        bytes' multiples for TMA, gate and up interleaved in groups of 8 (SiLU rides in the product's epilogue; the clamped
+        activation is a pass of its own between the two products)."""
+        return (self.MOE_TCGEN05 and not self.LIBRARY_GEMM_ONLY and dtype == torch.bfloat16
+                and activation in ("silu", "clamped_swish") and hidden % 8 == 0 and inter % 8 == 0)
 
     def moe_grouped_gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, tiles: torch.Tensor,
                             gated: bool) -> None:
@@ -1270,9 +1276,29 @@ class CudaKernels:
 
     def sink_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window, sink=None,
                        gate=None, plan=None) -> None:
-        """Attention with an optional sink and output gate, served by whichever kernel takes these sizes."""
+        """Attention with an optional sink and output gate, served by whichever kernel takes these sizes: in bfloat16
+        with heads of 64 or 128 the tensor-core kernels (``csrc/attention_mma.cu``; the gate is then a pass of its own), else
+        the general kernel with the gate in its epilogue.  ``plan``: what ``sink_attention_plan`` answered for a captured graph."""
+        if self.SINK_ATTENTION_MMA and q.dtype == torch.bfloat16 and head_dim in (64, 128) and scale > 0 and num_heads // num_kv_heads <= 16:
+            n_split = plan["n_split"] if plan else None
+            if n_split is None and meta.max_q_len * (num_heads // num_kv_heads) <= 16:
+                n_split = self.attention_splits(meta.num_seqs, num_kv_heads, min(meta.max_ctx, window) if window else meta.max_ctx)
+            self.paged_attention_mma(q, k_cache, v_cache, out, meta, num_heads=num_heads, num_kv_heads=num_kv_heads,
+                                     head_dim=head_dim, scale=scale, window=window, n_split=n_split, sink=sink)
+            if gate is not None:
+                self.sigmoid_mul(out, gate, out)
+            return
         self.paged_attention_sink(q, k_cache, v_cache, out, meta, num_heads=num_heads, num_kv_heads=num_kv_heads,
                                   head_dim=head_dim, scale=scale, window=window, sink=sink, gate=gate)
+
+    SINK_ATTENTION_MMA = os.environ.get("IIAN_SINK_ATTENTION_MMA", "1") not in ("0", "false", "off")
+
+    def sink_attention_plan(self, num_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, max_ctx: int,
+                            window: Optional[int], dtype: torch.dtype):
+        """The number of key parts of the decode form is part of a captured graph (grid and cluster sizes)."""
+        if dtype != torch.bfloat16 or head_dim not in (64, 128) or not self.SINK_ATTENTION_MMA:
+            return None
+        return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, window) if window else max_ctx)}
 
     # ---- the matrix-memory recurrence (csrc/matrix_memory.cu) ------------------------------------------------------------------
     def matrix_memory_scan(self, proj: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, gate_bias: torch.Tensor,

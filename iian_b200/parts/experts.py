@@ -101,6 +101,8 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(ws, dim=0).contiguous()
 
     def kernel_libraries(self):
+        if self.activation == "clamped_swish" and self.dtype == torch.bfloat16:
+            return ("moe", "gemm_simt", "postnorm")      # the activation between the two tcgen05 products
         return ("moe", "gemm_simt")        # in bfloat16 the products' fast forms come with gemm_simt (the grouped tcgen05 one too)
 
     def forward(self, x, ctx, with_extra: bool = False, rows=None):
@@ -135,7 +137,12 @@ class RoutedExperts(FeedForward):
         k.moe_scatter(x, pos, wts if on_input else None, xs, top)
         act = ctx.buf("expert_act", (m, self.inter), self.dtype)
         ys = ctx.buf("expert_out", (m, self.hidden), self.dtype)
-        if on_tc:
+        if on_tc and self.activation != "silu":
+            wide = ctx.buf("expert_gate_up", (m, 2 * self.inter), self.dtype)
+            k.moe_grouped_gemm_tc(xs, self.w_gate_up, wide, offsets, tiles, gated=False)
+            k.gated_act(wide, act, 8, self.activation, self.limit)
+            k.moe_grouped_gemm_tc(act, self.w_down, ys, offsets, tiles, gated=False)
+        elif on_tc:
             k.moe_grouped_gemm_tc(xs, self.w_gate_up, act, offsets, tiles, gated=True)
             k.moe_grouped_gemm_tc(act, self.w_down, ys, offsets, tiles, gated=False)
         else:

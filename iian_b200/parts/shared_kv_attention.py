@@ -80,7 +80,8 @@ class SharedKVAttention(Mixer):
         return KVNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
     def kernel_libraries(self):
-        return ("shared_kv", "attention_generic", "gemm_simt")
+        fast = self.dtype == torch.bfloat16 and self.hd in (64, 128)         # the tensor-core kernels take these heads
+        return ("shared_kv", "attention_generic", "gemm_simt") + (("attention_mma", "stream_ops") if fast else ())
 
     def graph_plan(self, num_seqs: int, max_ctx: int):
         k = ops.kernels()

@@ -153,7 +153,7 @@ def test_attention_sees_window_and_sink_exactly(dtype, nh, nkv, hd, window, page
     """Two keys are made to stand out by putting a multiple of a query into their cache cells (the norm over the projection
     would undo a scaled input): one just inside and one just outside the last token's window (without a window: at position
     1, hundreds of tokens back).  Queries: a portion of the last 7 tokens, then the same tokens one by one, then the first ones."""
-    n = 300
+    n = 300 if window else 1500                 # without a window: enough keys that decoding cuts them into several parts
     w = window or n
     inside, outside = (max(n - w, 1), n - w - 1) if window else (1, -1)
     c = _fill_cache(dtype, nh, nkv, hd, min(hd, 16) // 2 * 2, 1, list(range(n)), page, seed=nh * hd)
@@ -171,7 +171,7 @@ def test_attention_sees_window_and_sink_exactly(dtype, nh, nkv, hd, window, page
     assert p[:, n - 1, inside].max() > 0.2, "the stand-out key inside the window must matter"
     if outside >= 0:
         assert p[:, n - 1, outside].max() == 0 and p[:, n - 2, outside].max() > 0.2     # one token earlier it was still seen
-    bt = torch.full((1, 64), -1, dtype=torch.int32)
+    bt = torch.full((1, max(64, c.order.numel())), -1, dtype=torch.int32)
     bt[0, : c.order.numel()] = c.order
     gate = c.proj.to(DEV)[:, (nh + nkv) * hd:]
     for rows in (list(range(n - 7, n)), [n - 2], [n - 1], list(range(0, 3))):
