@@ -243,6 +243,172 @@ def run(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     return out
 
 
+def run_lekilix(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
+    """The kernels of the Lekilix design alone, each beside the like kernel of the Qwen3 path at equal size (16 heads of 128 on
+    8 KV heads, window 4,096; memories of 8 heads, 128 deep and 256 wide):
+      decode attention    8 (and 64) sequences of 4,096 cached tokens: with the sink  vs  without      bytes of cache read
+      prefill attention   one sequence of 2,048 tokens                                                  flops of scores and values
+      norm + rotation     2,048 tokens: norm over the whole projection, values = keys  vs  per-head norm, separate values
+      sum + norm          2,048 rows: two sub-layer outputs in the sum  vs  one
+      expert products     2,048 tokens x 6 of 64 experts by table (1,408 wide)  vs  the dense products of 8,448
+      memory scan         8 / 64 sequences of one token (bytes of state) and one sequence of 2,048 tokens (no like kernel)
+    """
+    import torch
+    from .. import ops
+    from ..config.spec import PartSpec
+    from ..engine.runner import StepContext, Workspace
+    from ..parts.experts import RoutedExperts
+    from ..parts.matrix_memory import state_block_floats, state_columns
+    k = ops.kernels()
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    nkv, hd, page, window = 8, 128, 16, 4096
+    out = {}
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+
+    def mem_row(name, ms, nbytes):
+        out[name] = {"ms": ms, "gb_s": nbytes / ms / 1e6, "of_hbm_peak": nbytes / ms / 1e6 / hbm}
+
+    def flop_row(name, ms, flops):
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "of_bf16_peak": flops / ms / 1e9 / tfl}
+
+    sink = torch.randn(heads, device=dev)
+    # ---- decode attention ------------------------------------------------------------------------------------------------
+    for B, ctx in ((8, 4096), (64, 4096)):
+        meta, pages = _meta([ctx] * B, [1] * B, page, dev)
+        copies = [(torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3, torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3)
+                  for _ in range(3 if B == 8 else 2)]
+        q = torch.randn(B, heads, hd, device=dev).to(bf) * 0.1
+        o = torch.empty(B, heads * hd, device=dev, dtype=bf)
+        nbytes = B * ctx * 2 * nkv * hd * 2
+        ms = _timed([(lambda c=c: k.sink_attention(q, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                   window=window, sink=sink)) for c in copies])
+        mem_row(f"decode_attention_sink_{B}x{ctx}", ms, nbytes)
+        ms = _timed([(lambda c=c: k.paged_attention(q, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                    window=window)) for c in copies])
+        mem_row(f"decode_attention_qwen3_{B}x{ctx}", ms, nbytes)
+        del copies
+    torch.cuda.empty_cache()
+    # ---- prefill attention -----------------------------------------------------------------------------------------------
+    T = 2048
+    meta, pages = _meta([T], [T], page, dev)
+    kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    q = torch.randn(T, heads, hd, device=dev).to(bf) * 0.1
+    o = torch.empty(T, heads * hd, device=dev, dtype=bf)
+    pairs = T * (T + 1) / 2
+    ms = _timed([lambda: k.sink_attention(q, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=window,
+                                          sink=sink)] * 4)
+    flop_row("prefill_attention_sink", ms, 4.0 * heads * hd * pairs)
+    ms = _timed([lambda: k.paged_attention(q, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=window)] * 4)
+    flop_row("prefill_attention_qwen3", ms, 4.0 * heads * hd * pairs)
+    # ---- norm, rotation, cache write ---------------------------------------------------------------------------------------
+    slots = torch.arange(T, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    wide = (2 * heads + nkv) * hd
+    sets = [(torch.randn(T, wide, device=dev).to(bf), torch.empty(T, heads, hd, device=dev, dtype=bf), torch.zeros_like(kc), torch.zeros_like(vc))
+            for _ in range(4)]
+    qw, kw = torch.ones(heads * hd, device=dev), torch.ones(nkv * hd, device=dev)
+    inv64 = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -torch.arange(32, dtype=torch.float64) / 32).to(dev)
+    ms = _timed([(lambda t=t: k.projection_norm_rope_store(t[0], 0, heads * hd, t[1], t[2], t[3], num_heads=heads, num_kv_heads=nkv,
+                                                           head_dim=hd, q_weight=qw, k_weight=kw, eps=1e-6, inv_freq=inv64, rot_dim=64,
+                                                           rope_style=1, positions=pos, slots=slots)) for t in sets])
+    mem_row("projection_norm_rope_store", ms, T * (heads + nkv) * hd * 2 + T * (heads + 2 * nkv) * hd * 2)
+    sets2 = [(torch.randn(T, (heads + 2 * nkv) * hd, device=dev).to(bf), t[1], t[2], t[3]) for t in sets]
+    qw2, kw2 = torch.ones(hd, device=dev), torch.ones(hd, device=dev)
+    inv_full = torch.pow(torch.tensor(500000.0), -torch.arange(hd // 2, dtype=torch.float32) / (hd // 2)).to(dev)
+    ms = _timed([(lambda t=t: k.qk_norm_rope_store(t[0], t[1], t[2], t[3], num_heads=heads, num_kv_heads=nkv, head_dim=hd, q_weight=qw2,
+                                                   k_weight=kw2, eps=1e-6, inv_freq=inv_full, rot_dim=hd, rope_style=0, positions=pos,
+                                                   slots=slots, write_kv=True)) for t in sets2])
+    mem_row("qk_norm_rope_store_qwen3", ms, 2 * T * (heads + 2 * nkv) * hd * 2)
+    del sets, sets2, kc, vc
+    # ---- sum + norm ------------------------------------------------------------------------------------------------------------
+    n = 2048
+    w = torch.ones(width, device=dev)
+    sets = [(torch.randn(n, width, device=dev), torch.randn(n, width, device=dev).to(bf), torch.randn(n, width, device=dev).to(bf),
+             torch.empty(n, width, device=dev, dtype=bf)) for _ in range(8)]
+    ms = _timed([(lambda t=t: k.add2_rms_norm(t[0], t[1], t[2], w, 1e-6, t[3])) for t in sets])
+    mem_row("add2_rms_norm", ms, n * width * (4 + 2 + 2 + 4 + 2))
+    ms = _timed([(lambda t=t: k.add_rms_norm(t[0], t[1], w, 1e-6, t[3])) for t in sets])
+    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 2))
+    del sets
+    # ---- expert products beside the dense products of the same active size ---------------------------------------------------------
+    E, top, ff, vocab = 64, 6, 1408, 32768
+    part = RoutedExperts(PartSpec("routed_experts", {"hidden_size": width, "num_experts": E, "top": top, "intermediate_size": ff,
+                                                     "activation": "clamped_swish", "limit": 7.0, "score": "table", "vocab_size": vocab,
+                                                     "weight_on": "output"}), bf, dev)
+    tensors = {"table": torch.stack([torch.randperm(E)[:top] for _ in range(vocab)]).to(torch.int32).to(dev)}
+    for e in range(E):
+        tensors[f"e{e}.gate"] = torch.randn(ff, width, device=dev).to(bf) * 0.02
+        tensors[f"e{e}.up"] = torch.randn(ff, width, device=dev).to(bf) * 0.02
+        tensors[f"e{e}.down"] = torch.randn(width, ff, device=dev).to(bf) * 0.02
+    part.bind(tensors)
+    del tensors
+    for n in (2048, 8):
+        h = torch.randn(n, width, device=dev).to(bf)
+        ctx_ = StepContext(Workspace(dev))
+        ctx_.tokens = torch.randint(0, vocab, (n,), device=dev).to(torch.int32)
+        part.forward(h, ctx_)
+        m = n * top
+        ms_all = _timed(lambda: part.forward(h, ctx_))
+        inter = top * ff
+        wgu = torch.randn(2 * inter, width, device=dev).to(bf) * 0.02
+        wd = torch.randn(width, inter, device=dev).to(bf) * 0.02
+        a2, y2 = torch.empty(n, inter, device=dev, dtype=bf), torch.empty(n, width, device=dev, dtype=bf)
+        fused = k.can_fuse_swiglu(h, wgu, 8)
+        gu = torch.empty(n, 2 * inter, device=dev, dtype=bf)
+        wgus = [wgu] + [wgu.clone() for _ in range(2 if n < 128 else 0)]
+        wds = [wd] + [wd.clone() for _ in range(2 if n < 128 else 0)]
+
+        def dense_on(wa, wb):
+            def run_():
+                if fused:
+                    k.linear_swiglu(h, wa, a2)
+                else:
+                    k.linear(h, wa, gu)
+                    k.swiglu(gu, a2, 8)
+                k.linear(a2, wb, y2)
+            return run_
+        ms_dense = _timed([dense_on(a, b) for a, b in zip(wgus, wds)] * (1 if n < 128 else 3))
+        if n >= 128:
+            flop_row(f"expert_feed_forward_{n}", ms_all, 2.0 * m * 3 * ff * width)
+            flop_row(f"dense_feed_forward_{n}", ms_dense, 2.0 * n * 3 * inter * width)
+        else:
+            reached = len(set(ctx_.buf("expert_ids", (n, top), torch.int32).flatten().tolist()))
+            mem_row(f"expert_feed_forward_{n}", ms_all, reached * 3 * ff * width * 2)
+            mem_row(f"dense_feed_forward_{n}", ms_dense, 3 * inter * width * 2)
+        del wgus, wds, wgu, wd
+    del part
+    torch.cuda.empty_cache()
+    # ---- the matrix-memory scan and what follows it ----------------------------------------------------------------------------------
+    H, d, dv, cap = heads // 2, 128, 256, 15.0
+    cb = state_columns(d, dv)
+    wide = 2 * H * d + 2 * H * dv
+    bias = torch.zeros(2 * H, device=dev)
+    for B, L in ((8, 1), (64, 1), (1, 2048)):
+        n = B * L
+        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, 2 * H, device=dev),
+                 torch.zeros(B, H, dv // cb, state_block_floats(d, cb), device=dev), torch.empty(n, H * dv, device=dev))
+                for _ in range(4 if L == 1 else 1)]
+        cu = torch.arange(0, n + 1, L, dtype=torch.int32, device=dev)
+        sl = torch.arange(B, dtype=torch.int32, device=dev)
+        ms = _timed([(lambda t=t: k.matrix_memory_scan(t[0], 0, H * d, 2 * H * d, t[1], bias, t[2], cu, sl, t[3], num_heads=H, dim=d,
+                                                       v_dim=dv, columns=cb, cap=cap, q_scale=d ** -0.5)) for t in sets])
+        if L == 1:
+            mem_row(f"memory_scan_decode_{B}", ms, B * 2 * H * (d * dv + d) * 4)
+        else:
+            flop_row(f"memory_scan_prefill_{L}", ms, 4.0 * L * H * d * (dv + 1))
+        if L > 1:
+            gate = sets[0][0][:, 2 * H * d + H * dv:]
+            wn = torch.ones(H * dv, device=dev)
+            o16 = torch.empty(n, H * dv, device=dev, dtype=bf)
+            ms = _timed([lambda: k.head_norm_gate(sets[0][3], wn, gate, o16, num_heads=H, eps=1e-6)] * 4)
+            mem_row("head_norm_gate", ms, n * H * dv * (4 + 2 + 2))
+        del sets
+    k.check_device_status()
+    return out
+
+
 def main(argv=None) -> int:
     from . import workloads
     peaks, kind = workloads.load_peaks()

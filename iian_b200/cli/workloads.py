@@ -65,6 +65,31 @@ EQUAL_QWEN3: Dict[str, dict] = {
     "g2k-moe": _qwen3_shape(2048, 16, 8, 6 * 1408),
     "g4k-dense": _qwen3_shape(4096, 32, 8, 12288),
 }
+
+
+def _lekilix_shape(width, heads, ff=0, experts=0, top=0, expert_ff=0, vocab=32768, window=4096):
+    """Six layers, memory and attention in turn, of which the first two run twice (eight layer runs, as the Qwen3 shape beside
+    it has eight layers): attention heads of 128 on 8 key/value heads, memories of half as many heads, 128 deep and 256 wide."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                          "rot": {"dims": 64, "base": 500000.0}, "mask": {"size": window}}}
+    mem = {"type": "mlstm", "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "gate_cap": 15.0}}
+    mlp = ({"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top}} if experts
+           else {"kind": "dense", "ff": ff})
+    return {"architecture": "Lekilix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [dict(mem if i % 2 == 0 else att, mlp=dict(mlp)) for i in range(6)]}
+
+
+# Lekilix shapes with layer sizes of real models, and beside each the Qwen3 dense shape of equal width, heads, layer runs and
+# (active) feed-forward size.
+LEKILIX_SHAPES: Dict[str, dict] = {
+    "l2k-dense": _lekilix_shape(2048, 16, ff=8192),
+    "l2k-moe": _lekilix_shape(2048, 16, experts=64, top=6, expert_ff=1408),
+    "l4k-dense": _lekilix_shape(4096, 32, ff=12288),
+}
+EQUAL_QWEN3.update({"l2k-dense": _qwen3_shape(2048, 16, 8, 8192), "l2k-moe": _qwen3_shape(2048, 16, 8, 6 * 1408),
+                    "l4k-dense": _qwen3_shape(4096, 32, 8, 12288)})
+DESIGN_SHAPES = {"galodra": GALODRA_SHAPES, "lekilix": LEKILIX_SHAPES}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -92,10 +117,17 @@ def shape_config(name: str, layers: Optional[int] = None):
         if layers:
             raw["layers"] = raw["layers"][:layers]
         return galodra_config_from_dict(raw)
+    if name in LEKILIX_SHAPES:
+        from ..models.lekilix import lekilix_config_from_dict
+        raw = dict(LEKILIX_SHAPES[name])
+        if layers:
+            raw["layers"] = raw["layers"][:layers]
+            raw["loop"] = None if layers < raw["loop"]["stop"] else raw["loop"]
+        return lekilix_config_from_dict(raw)
     try:
         raw = dict(SHAPES[name])
     except KeyError:
-        raise ValueError(f"unknown shape '{name}' ({' | '.join(list(SHAPES) + list(GALODRA_SHAPES))})") from None
+        raise ValueError(f"unknown shape '{name}' ({' | '.join(list(SHAPES) + list(GALODRA_SHAPES) + list(LEKILIX_SHAPES))})") from None
     if layers:
         raw["num_hidden_layers"] = layers
     return qwen3_config_from_dict(raw)
@@ -106,12 +138,14 @@ def random_model(name: str, dtype: str = "bfloat16", device="cuda:0", seed: int 
     from ..config.registry import get_architecture
     from ..engine.model import Model
     cfg = shape_config(name, layers)
-    arch = "Galodra" if name in GALODRA_SHAPES else "Qwen3ForCausalLM"
+    arch = "Galodra" if name in GALODRA_SHAPES else "Lekilix" if name in LEKILIX_SHAPES else "Qwen3ForCausalLM"
     return Model.from_random(get_architecture(arch), cfg, seed=seed, dtype=dtype, device=device, norm_jitter=0.0)
 
 
 def accounting_for(cfg, dtype_bytes: int = 2):
     """Bytes and flops of a step for a configuration of any built-in architecture."""
+    if hasattr(cfg, "embedding_scale"):
+        return LekilixAccounting(cfg, dtype_bytes)
     return GalodraAccounting(cfg, dtype_bytes) if hasattr(cfg, "postln_alpha") else Accounting(cfg, dtype_bytes)
 
 
@@ -175,6 +209,60 @@ class GalodraAccounting:
             w = m.window or tokens
             pairs = tokens * (tokens + 1) / 2 if tokens <= w else w * (w + 1) / 2 + (tokens - w) * w
             total += 2.0 * m.heads * (2 * m.kv_rank + m.rot_dim) * pairs
+        return total
+
+
+class LekilixAccounting:
+    """Bytes and flops of a Lekilix step, layer run by layer run (a layer of the looped stretch counts every time it runs: its
+    weights do not stay in the L2 between two runs at these sizes).  A decode step reads every dense weight once per run, of
+    the experts those that the batch is expected to reach, of the K/V cache the cells inside the window, and reads and
+    writes every memory's float32 state."""
+
+    def __init__(self, cfg, dtype_bytes: int = 2):
+        self.cfg, self.b = cfg, dtype_bytes
+        self.head_w = cfg.vocab * cfg.width
+
+    def _layer(self, lc, batch: int):
+        """(weights read by a step of ``batch`` tokens, weights a token multiplies with) of one layer run."""
+        w, m = self.cfg.width, lc.mixer
+        if lc.type == "attention":
+            mix = w * (2 * m.heads + m.kv_heads) * m.dim + m.heads * m.dim * w
+        else:
+            mix = w * (2 * m.heads * m.dim + 2 * m.heads * m.vdim + 2 * m.heads) + m.heads * m.vdim * w
+        if lc.mlp is None:
+            return mix, mix
+        if lc.mlp.kind == "dense":
+            return mix + 3 * w * lc.mlp.ff, mix + 3 * w * lc.mlp.ff
+        e, top = lc.mlp.experts, lc.mlp.top
+        reached = e * (1.0 - (1.0 - top / e) ** batch)
+        return mix + reached * 3 * w * lc.mlp.ff, mix + top * 3 * w * lc.mlp.ff
+
+    def _runs(self):
+        return [(self.cfg.layers[i], starts) for i, starts in self.cfg.run_order()]
+
+    def decode_bytes(self, batch: int, ctx_avg: float) -> float:
+        total = self.head_w * self.b
+        for lc, starts in self._runs():
+            total += (self._layer(lc, batch)[0] + (2 * self.cfg.width ** 2 if starts else 0)) * self.b
+            m = lc.mixer
+            if lc.type == "attention":
+                keys = min(ctx_avg, m.window) if m.window else ctx_avg
+                total += batch * keys * 2 * m.kv_heads * m.dim * self.b
+            else:
+                total += batch * 2 * m.heads * (m.dim * m.vdim + m.dim) * 4
+        return total
+
+    def prefill_flops(self, tokens: int) -> float:
+        total = 2.0 * self.head_w
+        for lc, starts in self._runs():
+            m = lc.mixer
+            total += 2.0 * tokens * (self._layer(lc, 1)[1] + (2 * self.cfg.width ** 2 if starts else 0))
+            if lc.type == "attention":
+                w = m.window or tokens
+                pairs = tokens * (tokens + 1) / 2 if tokens <= w else w * (w + 1) / 2 + (tokens - w) * w
+                total += 4.0 * m.heads * m.dim * pairs
+            else:
+                total += 4.0 * tokens * m.heads * m.dim * (m.vdim + 1)         # the update and the read-out of every token
         return total
 
 
@@ -403,9 +491,9 @@ def serving_workload(shape: str = "0.6b", n_requests: int = 256, kv_cache_tokens
 
 # ---- one design beside another of equal size ------------------------------------------------------------------------
 def design_comparison(names: Sequence[str], batches: Sequence[int], prefill_tokens: Sequence[int], prompt_len: int, steps: int,
-                      warmup: int, peaks: dict, device="cuda:0", cuda_graphs: bool = True) -> dict:
-    """Decode and prefill throughput of each named Galodra shape and of the Qwen3 shape of equal size, random weights:
-    ``{name: {"galodra": {...}, "qwen3": {...}}}`` with tokens/s and roofline fractions per point."""
+                      warmup: int, peaks: dict, device="cuda:0", cuda_graphs: bool = True, design: str = "galodra") -> dict:
+    """Decode and prefill throughput of each named shape of ``design`` and of the Qwen3 shape of equal size, random weights:
+    ``{name: {design: {...}, "qwen3": {...}}}`` with tokens/s and roofline fractions per point."""
     import gc
     import torch
     from ..config.registry import get_architecture
@@ -414,8 +502,8 @@ def design_comparison(names: Sequence[str], batches: Sequence[int], prefill_toke
     out = {}
     for name in names:
         row = {}
-        for side in ("galodra", "qwen3"):
-            if side == "galodra":
+        for side in (design, "qwen3"):
+            if side == design:
                 model = random_model(name, "bfloat16", device)
             else:
                 model = Model.from_random(get_architecture("Qwen3ForCausalLM"), qwen3_config_from_dict(EQUAL_QWEN3[name]), seed=0,

@@ -48,6 +48,9 @@ struct TcAttnParams {
     int max_blocks, nh, nkv, page_size, num_pages, window;
     float scale_log2;               // scale * log2(e)
     int * status;                   // {code, where}; zero before the launch
+    // a sink per head: a logit without key and value that joins the softmax's denominator once, not scaled
+    const float * sink = nullptr;   // [nh] or null
+    float sink_to_raw = 0.0f;       // 1 / scale: maxima are kept of raw scores, the scale enters in the exponent
 };
 
 __device__ __forceinline__ unsigned at_smem(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -362,6 +365,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         const unsigned tS = tmem_base + (unsigned) (g * 128), tO = tmem_base + 256u + (unsigned) (g * 128);
         const int n_mine = n_grp[g];
         float m_run = -INFINITY, l_run = 0.0f;
+        if (p.sink != nullptr && row_ok) {      // the running softmax starts at the sink: maximum sink, sum 1, nothing in O
+            m_run = p.sink[kvh * G + R % G] * p.sink_to_raw;
+            l_run = 1.0f;
+        }
         const float sl = p.scale_log2;
         bool failed = false;
         for (int i = 0; i < n_mine; i++) {
@@ -529,11 +536,26 @@ using namespace iian;
 // Prefill attention on tcgen05: head size 128, bf16, page sizes 8, 16, 32, 64 or 128 (a page is one TMA box; 8 rows
 // are one swizzle atom).  q [N, nh, 128], caches [num_pages, nkv, page_size, 128], out [N, nh * 128].  status: two
 // ints on the device, zero before the launch; non-zero afterwards means a wait gave up and the output is not valid.
+IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const void * v_cache, void * out,
+                                    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                    float scale, int window, int * status, const float * sink, cudaStream_t stream);
+
 IIAN_API int iian_attention_tc(const void * q, const void * k_cache, const void * v_cache, void * out,
                                const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
                                int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
                                float scale, int window, int * status, cudaStream_t stream) {
+    return iian_attention_tc_sink(q, k_cache, v_cache, out, cu_q, ctx_len, block_table, max_blocks, N, S, max_q_len, nh, nkv, hd,
+                                  page_size, num_pages, scale, window, status, nullptr, stream);
+}
+
+// The same with a sink per head in the softmax's denominator (sink: f32 [nh], or null; needs scale > 0).
+IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const void * v_cache, void * out,
+                                    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                    float scale, int window, int * status, const float * sink, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
+    if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
     if (hd != AT_HD || nkv <= 0 || nh % nkv != 0) return IIAN_ERR_SHAPE;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return IIAN_ERR_SHAPE;
     if (status == nullptr) return IIAN_ERR_SHAPE;
@@ -549,6 +571,8 @@ IIAN_API int iian_attention_tc(const void * q, const void * k_cache, const void 
     p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.sink = sink;
+    p.sink_to_raw = sink != nullptr ? 1.0f / scale : 0.0f;
     const size_t smem = (size_t) 6 * AT_TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {

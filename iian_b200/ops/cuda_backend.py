@@ -603,8 +603,10 @@ class CudaKernels:
                 and k_cache.shape[2] in (8, 16, 32, 64, 128) and nkv > 0 and nh % nkv == 0
                 and meta.max_q_len * (nh // nkv) >= self.TC_ATTENTION_MIN_ROWS)
 
-    def paged_attention_tc(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window) -> None:
-        """Prefill attention on tcgen05 + TMA: head size 128, bfloat16, pages of 8 to 128 tokens."""
+    def paged_attention_tc(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window,
+                           sink: Optional[torch.Tensor] = None) -> None:
+        """Prefill attention on tcgen05 + TMA: head size 128, bfloat16, pages of 8 to 128 tokens.  ``sink``: float32 [heads],
+        a logit per head that joins the softmax's denominator (needs ``scale`` > 0)."""
         n = q.shape[0]
         if k_cache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("paged_attention_tc: bfloat16 only")
@@ -613,14 +615,16 @@ class CudaKernels:
         status = self.tcgen05_status_buffer(q.device)
         CudaKernels._tc_used = True
         bt = meta.block_table
-        fn = _fn("attention_tc", "iian_attention_tc",
+        if sink is not None and sink.numel() != num_heads:
+            raise KernelError("paged_attention_tc: one sink per head")
+        fn = _fn("attention_tc", "iian_attention_tc_sink",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
         _check(fn(_cuda(q, "q"), _cuda(k_cache, "k cache"), _cuda(v_cache, "v cache"), _cuda(out, "attention out"),
                   _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, num_heads,
                   num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0,
-                  status.data_ptr(), _stream()), "attention_tc")
+                  status.data_ptr(), _cuda(sink, "sink", torch.float32), _stream()), "attention_tc")
 
     def _attention_dispatch(self, q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, window, n_split=None) -> None:
         if self._attention_tc_ok(q, k_cache, meta, nh, nkv, hd):
@@ -1277,8 +1281,15 @@ class CudaKernels:
     def sink_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, head_dim, scale, window, sink=None,
                        gate=None, plan=None) -> None:
         """Attention with an optional sink and output gate, served by whichever kernel takes these sizes: in bfloat16
-        with heads of 64 or 128 the tensor-core kernels (``csrc/attention_mma.cu``; the gate is then a pass of its own), else
+        with heads of 64 or 128 the tensor-core kernels (``csrc/attention_tc.cu`` for portions of prompts with heads of 128,
+        ``csrc/attention_mma.cu`` otherwise; the gate is then a pass of its own), else
         the general kernel with the gate in its epilogue.  ``plan``: what ``sink_attention_plan`` answered for a captured graph."""
+        if self.SINK_ATTENTION_MMA and scale > 0 and self._attention_tc_ok(q, k_cache, meta, num_heads, num_kv_heads, head_dim):
+            self.paged_attention_tc(q, k_cache, v_cache, out, meta, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                                    scale=scale, window=window, sink=sink)          # portions of prompts, heads of 128: tcgen05
+            if gate is not None:
+                self.sigmoid_mul(out, gate, out)
+            return
         if self.SINK_ATTENTION_MMA and q.dtype == torch.bfloat16 and head_dim in (64, 128) and scale > 0 and num_heads // num_kv_heads <= 16:
             n_split = plan["n_split"] if plan else None
             if n_split is None and meta.max_q_len * (num_heads // num_kv_heads) <= 16:

@@ -81,7 +81,7 @@ class SharedKVAttention(Mixer):
 
     def kernel_libraries(self):
         fast = self.dtype == torch.bfloat16 and self.hd in (64, 128)         # the tensor-core kernels take these heads
-        return ("shared_kv", "attention_generic", "gemm_simt") + (("attention_mma", "stream_ops") if fast else ())
+        return ("shared_kv", "attention_generic", "gemm_simt") + ((("attention_mma", "stream_ops") + (("attention_tc",) if self.hd == 128 else ())) if fast else ())
 
     def graph_plan(self, num_seqs: int, max_ctx: int):
         k = ops.kernels()

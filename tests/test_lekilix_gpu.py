@@ -148,7 +148,7 @@ def _plain_attention(c, nh, nkv, hd, scale, window, sink, gate):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh, nkv, hd, window, page", [(6, 2, 16, 37, 16), (4, 4, 64, 33, 8), (8, 2, 64, 64, 16), (2, 1, 128, None, 32),
-                                                      (3, 1, 24, 5, 16)])
+                                                      (3, 1, 24, 5, 16), (4, 2, 128, 150, 16)])
 def test_attention_sees_window_and_sink_exactly(dtype, nh, nkv, hd, window, page):
     """Two keys are made to stand out by putting a multiple of a query into their cache cells (the norm over the projection
     would undo a scaled input): one just inside and one just outside the last token's window (without a window: at position
@@ -174,7 +174,7 @@ def test_attention_sees_window_and_sink_exactly(dtype, nh, nkv, hd, window, page
     bt = torch.full((1, max(64, c.order.numel())), -1, dtype=torch.int32)
     bt[0, : c.order.numel()] = c.order
     gate = c.proj.to(DEV)[:, (nh + nkv) * hd:]
-    for rows in (list(range(n - 7, n)), [n - 2], [n - 1], list(range(0, 3))):
+    for rows in (list(range(n - 7, n)), [n - 2], [n - 1], list(range(0, 3)), list(range(n - 200, n)), list(range(0, 130))):
         r = torch.tensor(rows)
         meta = SimpleNamespace(positions=c.pos[r].to(DEV), seq_of_token=torch.zeros(len(rows), dtype=torch.int32, device=DEV),
                                cu_q=torch.tensor([0, len(rows)], dtype=torch.int32, device=DEV),
