@@ -393,7 +393,7 @@ def run_lekilix(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
         cu = torch.arange(0, n + 1, L, dtype=torch.int32, device=dev)
         sl = torch.arange(B, dtype=torch.int32, device=dev)
         ms = _timed([(lambda t=t: k.matrix_memory_scan(t[0], 0, H * d, 2 * H * d, t[1], bias, t[2], cu, sl, t[3], num_heads=H, dim=d,
-                                                       v_dim=dv, columns=cb, cap=cap, q_scale=d ** -0.5)) for t in sets])
+                                                       v_dim=dv, columns=cb, cap=cap, q_scale=d ** -0.5, max_q_len=L)) for t in sets])
         if L == 1:
             mem_row(f"memory_scan_decode_{B}", ms, B * 2 * H * (d * dv + d) * 4)
         else:

@@ -1314,10 +1314,11 @@ class CudaKernels:
     # ---- the matrix-memory recurrence (csrc/matrix_memory.cu) ------------------------------------------------------------------
     def matrix_memory_scan(self, proj: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, gate_bias: torch.Tensor,
                            state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, *, num_heads: int,
-                           dim: int, v_dim: int, columns: int, cap: float, q_scale: float) -> None:
+                           dim: int, v_dim: int, columns: int, cap: float, q_scale: float, max_q_len: int = 0) -> None:
         """Walk every sequence's tokens of this step through the recurrence, from and into ``state`` [slots, heads,
         v_dim / columns, block floats] (float32).  ``proj`` rows hold q, k, v at the given column offsets; ``gates`` float32
-        [N, 2 heads] the input- and forget-gate pre-activations, ``gate_bias`` [2 heads]; ``out`` float32 [N, heads * v_dim]."""
+        [N, 2 heads] the input- and forget-gate pre-activations, ``gate_bias`` [2 heads]; ``out`` float32 [N, heads * v_dim].
+        ``max_q_len``: the most tokens a sequence brings (a hint: 1 picks the kernel's form for single tokens; 0: unknown)."""
         n = proj.shape[0]
         pp, ld = self._rows(proj, "projections")
         s = cu_q.numel() - 1
@@ -1328,11 +1329,11 @@ class CudaKernels:
             raise KernelError(f"matrix_memory_scan: state {tuple(state.shape)} does not match {num_heads} heads of {dim} x {v_dim}")
         fn = _fn("matrix_memory", "iian_matrix_memory_scan",
                  [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                  c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+                  c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
         _check(fn(pp, ld, q_off, k_off, v_off, _cuda(gates, "gates", torch.float32), _cuda(gate_bias, "gate bias", torch.float32),
                   _cuda(state, "state", torch.float32), _cuda(cu_q, "cu_q", torch.int32), _cuda(state_slots, "state slots", torch.int32),
                   _cuda(out, "memory out", torch.float32), _code(proj, "projections"), s, num_heads, dim, v_dim, columns, cap,
-                  q_scale, _stream()), "matrix_memory_scan")
+                  q_scale, max_q_len, _stream()), "matrix_memory_scan")
 
     @staticmethod
     def matrix_memory_lanes(dim: int) -> int:

@@ -110,7 +110,7 @@ class MatrixMemory(Mixer):
         heads = ctx.buf("memory_heads", (n, self.v_size), torch.float32)
         k.matrix_memory_scan(proj, 0, self.qk_size, 2 * self.qk_size, gates, self.gate_bias, cache.state, ctx.cu_q,
                              ctx.state_slots, heads, num_heads=self.nh, dim=self.dim, v_dim=self.vdim, columns=self.columns,
-                             cap=self.cap, q_scale=self.dim ** -0.5)
+                             cap=self.cap, q_scale=self.dim ** -0.5, max_q_len=ctx.max_q_len)
         gate = proj[:, 2 * self.qk_size + self.v_size:] if self.has_gate else None
         normed = ctx.buf("memory_normed", (n, self.v_size), self.dtype)
         k.head_norm_gate(heads, self.norm_w, gate, normed, num_heads=self.nh, eps=self.eps)

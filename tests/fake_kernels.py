@@ -122,7 +122,7 @@ class FakeKernels:
         out.copy_(o.to(out.dtype))
 
     def matrix_memory_scan(self, proj, q_off, k_off, v_off, gates, gate_bias, state, cu_q, state_slots, out, *, num_heads, dim,
-                           v_dim, columns, cap, q_scale):
+                           v_dim, columns, cap, q_scale, max_q_len=0):
         H, d, dv, cb = num_heads, dim, v_dim, columns
         nblk = dv // cb
         for s in range(state_slots.numel()):
