@@ -43,6 +43,8 @@ def layer(mix, mlp):
 #    and three; a window of 33; a memory wider than it is deep.
 # W: no loop at all; one head, one expert of one; no rotation in one layer; a window shorter than a page and one longer than
 #    any request; a memory deep enough for the 16-lane form of the scan.
+# X: heads of 128 (the tensor-core attention kernels of the large shapes, tcgen05 for portions), a memory 128 deep, the
+#    first two layers run twice.   Y: a width and sizes that are multiples of 4 only (no 16-byte rows for the fast products).
 CONFIGS = {
     "U": {"architecture": "Lekilix", "vocab": 211, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.7},
           "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [
@@ -61,8 +63,18 @@ CONFIGS = {
         layer(attention(2, 1, 32, 70, 0, 0.2), None),
         layer(memory(1, 8, 8, 20.0), None)]},
 }
-BLOCK_SIZE = {"U": 16, "V": 8, "W": 32}
-SEED = {"U": 21, "V": 22, "W": 23}
+CONFIGS["X"] = {"architecture": "Lekilix", "vocab": 331, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 16.0},
+                "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [
+    layer(attention(4, 2, 128, 40, 64, 0.09, 500000.0), dense(384)),
+    layer(memory(2, 128, 64, 9.0), moe(4, 2, 64, 3.0)),
+    layer(attention(2, 2, 128, 90, 128, 0.07), moe(6, 1, 128, 1.2))]}
+CONFIGS["Y"] = {"architecture": "Lekilix", "vocab": 150, "width": 100, "norm": {"eps": 1e-5}, "embedding": {"scale": 10.0},
+                "loop": {"start": 1, "stop": 2, "times": 3}, "layers": [
+    layer(memory(5, 20, 12, 11.0), dense(52)),
+    layer(attention(5, 1, 20, 9, 10, 0.25), moe(3, 2, 36, 2.0)),
+    layer(memory(3, 12, 20, 7.0), None)]}
+BLOCK_SIZE = {"U": 16, "V": 8, "W": 32, "X": 16, "Y": 16}
+SEED = {"U": 21, "V": 22, "W": 23, "X": 24, "Y": 25}
 
 
 def write_case(tmp_path, name: str, store_dtype=torch.bfloat16, std: float = 0.08) -> str:

@@ -196,7 +196,7 @@ def cases(tmp_path_factory):
     return out
 
 
-LENGTHS = {"U": [1, 9, 40, 75], "V": [3, 35, 70, 20, 2], "W": [2, 90, 33]}
+LENGTHS = {"U": [1, 9, 40, 75], "V": [3, 35, 70, 20, 2], "W": [2, 90, 33], "X": [45, 5, 20], "Y": [41, 3, 30]}
 
 
 @pytest.mark.parametrize("name", sorted(CONFIGS))

@@ -298,7 +298,7 @@ def folders(tmp_path_factory):
     return {name: write_case(root, name) for name in CONFIGS}
 
 
-LENGTHS = {"U": [1, 9, 40, 75, 130], "V": [3, 35, 70, 20, 100], "W": [2, 90, 33, 150]}
+LENGTHS = {"U": [1, 9, 40, 75, 130], "V": [3, 35, 70, 20, 100], "W": [2, 90, 33, 150], "X": [70, 5, 120, 33], "Y": [41, 3, 77]}
 _plain_cache = {}
 
 
