@@ -11,9 +11,8 @@
 // The columns of C are independent of one another, so a CTA owns `cb` of them for one (sequence, head): a group of R
 // lanes per column holds that column (and a copy of n) in registers.  The gates do not depend on C, so one more warp (the
 // gate warp) runs their chain (m, the two decays, exp(-m)) a chunk of tokens ahead of the others and leaves them in
-// shared memory; the other threads fetch the next chunk's q, k and v rows into registers while they work on the
-// current chunk out of shared memory, and put them there when they are done: a step's loads never lie on the chain from
-// token to token.  A step then costs d / R fused multiply-adds times four per lane and two sums over R lanes by shuffles.
+// shared memory; loader threads fetch the next chunk's q, k and v rows and put them there while the column holders work
+// on the current chunk out of shared memory: a step's loads never lie on the chain from token to token.  A step then costs d / R fused multiply-adds times four per lane and two sums over R lanes by shuffles.
 // Every CTA of a (sequence, head) keeps its own copy of n and m in the state (a column block is `cb * d` floats of C
 // column by column, then d floats of n, then m, padded to a multiple of 4), so no CTA reads what another writes.
 // Gates, decays, state and sums are float32 whatever the activation type; the order of every sum is fixed by (d, R)
@@ -37,7 +36,7 @@ constexpr unsigned kMemTokShift = 27, kMemIsQ = 1u << 26, kMemSkip = 0xffffffffu
 // issued together -- only the update of C and n is a chain from token to token, one multiply-add deep, and the
 // read-outs of U tokens overlap each other and the next tokens' updates.  (PF, U) = (40, 4) for portions of prompts,
 // (4, 1) with chunks of one token for steps of single tokens: fewer registers, more CTAs on an SM.
-template <typename A, int MAXE, int R, int V, int PF, int U>
+template <typename A, int MAXE, int R, int V, int PF, int U, bool LOADERS>
 __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
     const A * __restrict__ proj, long long ld, int q_off, int k_off, int v_off, const float * __restrict__ gates,
     const float * __restrict__ gate_bias, float * __restrict__ state, const int * __restrict__ cu_q,
@@ -50,12 +49,18 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
     const int slot = state_slots[seq];
     const int tid = threadIdx.x;
-    const int n_cons = blockDim.x - 32;                  // the last warp is the gate warp
-    const bool gate_warp = tid >= n_cons;
+    // Roles: the threads that hold columns; one gate warp; and, with LOADERS (portions, up to 128 column holders), as many
+    // loader threads as column holders, which fetch and put down the next chunk so that the column holders do nothing but
+    // the recurrence.  Without them the column holders fetch their own rows (the form for single tokens: fewer threads,
+    // more CTAs on an SM; and CTAs of 256 column holders).
+    const int n_cons = LOADERS ? (blockDim.x - 32) / 2 : blockDim.x - 32;
+    const bool gate_warp = tid >= n_cons && tid < n_cons + 32;
+    const bool loader = LOADERS ? tid >= n_cons + 32 : tid < n_cons;     // who fetches
+    const int ltid = LOADERS ? tid - n_cons - 32 : tid;                  // its index among those who fetch
     const int r = tid % R;
     int c = tid / R;
-    const bool owner = !gate_warp && c < cb && r == 0;
-    const bool holds = !gate_warp && c < cb;
+    const bool owner = tid < n_cons && c < cb && r == 0;
+    const bool holds = tid < n_cons && c < cb;
     if (c >= cb) c = cb - 1;          // lanes beyond the block's columns repeat its last one and store nothing
     const int col = blk * cb + c;
     if (slot < 0) {                   // a padding sequence: no state, zeros out
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
     float * sb = state + (((size_t) slot * heads + head) * nblk + blk) * block_floats;
     float C[MAXE], n[MAXE];
     float m = 0.0f;
-    if (!gate_warp) {
+    if (tid < n_cons) {
 #pragma unroll
         for (int g = 0; g < MAXE / V; g++) {
             const int e0 = (g * R + r) * V;
@@ -97,7 +102,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
                 n[g] = e0 < d ? nv : 0.0f;
             }
         }
-    } else {
+    } else if (gate_warp) {
         m = sb[(size_t) (cb + 1) * d];
     }
     const float bias_i = gate_bias[head], bias_f = gate_bias[heads + head];
@@ -114,7 +119,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
         pf_ok = 0ull;
 #pragma unroll
         for (int k = 0; k < PF; k++) {
-            const int want = tid + k * n_cons;
+            const int want = ltid + k * n_cons;
             const unsigned e = tab[min(want, total - 1)];
             const int tt = (int) (e >> kMemTokShift);
             const bool ok = want < total && e != kMemSkip && tt < ntok;
@@ -127,7 +132,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
     auto stash = [&](float * buf) {
 #pragma unroll
         for (int k = 0; k < PF; k++) {
-            const int idx = tid + k * n_cons;
+            const int idx = ltid + k * n_cons;
             if (idx < total) buf[idx] = ((pf_ok >> k) & 1ull) ? pf[k] : 0.0f;
         }
     };
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
     };
 
     if (gate_warp) gate_chain(t0, buf0);
-    else { fetch(t0); stash(buf0); }
+    else if (loader) { fetch(t0); stash(buf0); }
     __syncthreads();
     int which = 0;
     for (int tc = t0; tc < t1; tc += chunk, which ^= 1) {
@@ -160,8 +165,10 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
         const bool more = tc + chunk < t1;
         if (gate_warp) {
             if (more) gate_chain(tc + chunk, nxt);
+        } else if (LOADERS && loader) {
+            if (more) { fetch(tc + chunk); stash(nxt); }
         } else {
-            if (more) fetch(tc + chunk);
+            if (!LOADERS && more) fetch(tc + chunk);
             const int ntok = min(chunk, t1 - tc);
             for (int tt0 = 0; tt0 < ntok; tt0 += U) {
                 float num[U], den[U], floor_[U];
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
                     if (owner && tt0 + u < ntok)
                         out[(size_t) (tc + tt0 + u) * heads * dv + head * dv + col] = num[u] / (fmaxf(fabsf(den[u]), floor_[u]) + 1e-6f);
             }
-            if (more) stash(nxt);
+            if (!LOADERS && more) stash(nxt);
         }
         __syncthreads();
     }
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(288) matrix_memory_scan_kernel(
             }
         }
     }
-    if (gate_warp && tid == n_cons) sb[(size_t) (cb + 1) * d] = m;
+    if (tid == n_cons) sb[(size_t) (cb + 1) * d] = m;
 }
 
 }  // namespace iian
@@ -270,19 +277,20 @@ IIAN_API int iian_matrix_memory_scan(const void * proj, long long ld, int q_off,
     typedef __nv_bfloat16 bf16;
 #define IIAN_MM(AT, MAXE, R, V)                                                                                                   \
     do {                                                                                                                          \
-        if (short_form) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetchShort, 1);                                                       \
-        IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4);                                                                            \
+        if (short_form) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetchShort, 1, false);                                                \
+        if (n_cons <= 128) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4, true);                                                   \
+        IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4, false);                                                                     \
     } while (0)
-#define IIAN_MM_FORM(AT, MAXE, R, V, PF, U)                                                                                       \
+#define IIAN_MM_FORM(AT, MAXE, R, V, PF, U, LD)                                                                                   \
     do {                                                                                                                          \
-        auto kernel = matrix_memory_scan_kernel<AT, MAXE, R, V, PF, U>;                                                           \
+        auto kernel = matrix_memory_scan_kernel<AT, MAXE, R, V, PF, U, LD>;                                                       \
         static size_t configured = 48 * 1024;                                                                                     \
         if (smem > configured) {                                                                                                  \
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);                \
             if (e != cudaSuccess) return 1000 + (int) e;                                                                          \
             configured = smem;                                                                                                    \
         }                                                                                                                         \
-        return iian_launch(kernel, grid, dim3(n_cons + 32), smem, stream, (const AT *) proj, ld, q_off, k_off, v_off, gates,      \
+        return iian_launch(kernel, grid, dim3((LD ? 2 * n_cons : n_cons) + 32), smem, stream, (const AT *) proj, ld, q_off, k_off, v_off, gates,      \
                            gate_bias, state, cu_q, state_slots, out, heads, d, dv, cb, bf, cap, q_scale, chunk);                  \
     } while (0)
 #define IIAN_MM_SIZES(AT)                                       \
