@@ -255,6 +255,25 @@ IIAN_API int iian_matrix_memory_block_floats(int d, int cb) { return ((cb + 1) *
 // so cb * lanes <= 256
 IIAN_API int iian_matrix_memory_lanes(int d) { return d <= 128 ? 8 : d <= 256 ? 16 : 32; }
 
+// Which form portions of prompts take: 1 with loader warps, 2 without, 0 (default) chosen by the launch: with loader warps a
+// CTA has 288 threads of 168 registers and an SM holds one; without, 160 threads and an SM holds two.  Loader warps win
+// while there is at most one CTA per SM to run (0.58 against 0.87 ms for 128 CTAs); beyond that two CTAs per SM do.
+static int g_mm_form = 0;
+IIAN_API int iian_matrix_memory_form(int form) {
+    if (form < 0 || form > 2) return IIAN_ERR_SHAPE;
+    g_mm_form = form;
+    return IIAN_OK;
+}
+
+static int mm_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
 IIAN_API int iian_matrix_memory_scan(const void * proj, long long ld, int q_off, int k_off, int v_off, const float * gates,
                                      const float * gate_bias, float * state, const int * cu_q, const int * state_slots,
                                      float * out, int act_dtype, int num_seqs, int heads, int d, int dv, int cb, float cap,
@@ -274,11 +293,13 @@ IIAN_API int iian_matrix_memory_scan(const void * proj, long long ld, int q_off,
     if ((chunk * rowp + n_cons - 1) / n_cons > kMemPrefetch) return IIAN_ERR_SHAPE;
     const size_t smem = ((size_t) chunk * rowp + 2 * ((size_t) chunk * rowp + chunk * 4)) * sizeof(float);
     dim3 grid(dv / cb, heads, num_seqs);
+    const long long ctas = (long long) (dv / cb) * heads * num_seqs;
+    const bool with_loaders = n_cons <= 128 && (g_mm_form == 1 || (g_mm_form == 0 && ctas <= mm_sm_count()));
     typedef __nv_bfloat16 bf16;
 #define IIAN_MM(AT, MAXE, R, V)                                                                                                   \
     do {                                                                                                                          \
         if (short_form) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetchShort, 1, false);                                                \
-        if (n_cons <= 128) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4, true);                                                   \
+        if (with_loaders) IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4, true);                                                    \
         IIAN_MM_FORM(AT, MAXE, R, V, kMemPrefetch, 4, false);                                                                     \
     } while (0)
 #define IIAN_MM_FORM(AT, MAXE, R, V, PF, U, LD)                                                                                   \
